@@ -1,0 +1,839 @@
+// Host side of the C ABI (include/cpu_ops_b200.h): argument validation in the
+// CPU library's order, operand staging, the choice of tile / split-k / operand
+// swap, tensor-map construction and kernel launches.
+//
+// It plays the role of the CPU library's device + kernel layers
+// (gemm/device/gemm.h:99-127, gemm/device/gemm_mx.h:78-118,
+// gemm/kernel/run_blocked.h:79-174) for a GPU: the thread partition becomes a
+// persistent grid of CTA tiles, the per-task pack buffers disappear (TMA feeds
+// the tensor cores from the caller's layout), the split-k workspace lives in a
+// cached device buffer.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <vector>
+
+#include "../../include/cpu_ops_b200.h"
+#include "aux_kernels.cuh"
+#include "gemm_kernel.cuh"
+#include "gemm_params.h"
+
+namespace {
+
+using namespace b200;
+
+thread_local char g_last_error[512] = "";
+std::atomic<uint64_t> g_launches{0};
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+}
+
+#define CUDA_TRY(expr)                                                                       \
+  do {                                                                                       \
+    cudaError_t err__ = (expr);                                                              \
+    if (err__ != cudaSuccess) {                                                              \
+      set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(err__), __FILE__, __LINE__); \
+      return CPUOPS_B200_STATUS_CUDA_ERROR;                                                  \
+    }                                                                                        \
+  } while (0)
+
+// ---- per-device state ---------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct DeviceState {
+  bool ready = false;
+  int device = -1;
+  int sm_count = 0;
+  int smem_optin = 0;
+  cudaStream_t stream = nullptr;  // the library's own stream
+  int32_t* error_dev = nullptr;   // device error word
+  int32_t* error_host = nullptr;  // pinned mirror
+  // grow-only workspaces, one per stream that ever called in
+  struct Workspace {
+    void* ptr = nullptr;
+    size_t bytes = 0;
+  };
+  std::map<cudaStream_t, Workspace> ws;
+};
+
+std::mutex g_mu;  // serialises calls (the CPU library serialises on its pool mutex too)
+DeviceState g_dev[64];
+EncodeTiledFn g_encode = nullptr;
+int g_device_count = -2;  // -2: not probed
+
+int probe_devices() {
+  if (g_device_count != -2) return g_device_count;
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) {
+    cudaGetLastError();
+    g_device_count = 0;
+    return 0;
+  }
+  int usable = 0;
+  for (int d = 0; d < n && d < 64; ++d) {
+    int major = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, d) == cudaSuccess &&
+        major == 10)
+      ++usable;
+  }
+  g_device_count = usable;
+  return usable;
+}
+
+int init_device(int device, DeviceState** out) {
+  if (probe_devices() <= 0) {
+    set_error("no sm_100 CUDA device is available; this library has no CPU fallback");
+    return CPUOPS_B200_STATUS_NO_DEVICE;
+  }
+  if (device < 0) CUDA_TRY(cudaGetDevice(&device));
+  if (device >= 64) {
+    set_error("device ordinal %d out of range", device);
+    return CPUOPS_B200_STATUS_BAD_DESCRIPTOR;
+  }
+  DeviceState& st = g_dev[device];
+  if (!st.ready) {
+    int major = 0;
+    CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+    if (major != 10) {
+      set_error("device %d is not sm_100 (compute capability major %d)", device, major);
+      return CPUOPS_B200_STATUS_NO_DEVICE;
+    }
+    CUDA_TRY(cudaSetDevice(device));
+    st.device = device;
+    CUDA_TRY(cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, device));
+    CUDA_TRY(cudaDeviceGetAttribute(&st.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+    CUDA_TRY(cudaStreamCreateWithFlags(&st.stream, cudaStreamNonBlocking));
+    CUDA_TRY(cudaMalloc(&st.error_dev, sizeof(int32_t)));
+    CUDA_TRY(cudaMemset(st.error_dev, 0, sizeof(int32_t)));
+    CUDA_TRY(cudaMallocHost(&st.error_host, sizeof(int32_t)));
+    *st.error_host = 0;
+    if (!g_encode) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult qres;
+      CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+      if (!fn || qres != cudaDriverEntryPointSuccess) {
+        set_error("cuTensorMapEncodeTiled is not exported by this driver");
+        return CPUOPS_B200_STATUS_CUDA_ERROR;
+      }
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindI8>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
+    CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindMxf8>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
+    CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindMxf4>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
+    st.ready = true;
+  } else {
+    CUDA_TRY(cudaSetDevice(device));
+  }
+  *out = &st;
+  return 0;
+}
+
+int ensure_workspace(DeviceState& st, cudaStream_t stream, size_t bytes, uint8_t** out) {
+  DeviceState::Workspace& w = st.ws[stream];
+  if (w.bytes < bytes) {
+    if (w.ptr) {
+      CUDA_TRY(cudaStreamSynchronize(stream));
+      CUDA_TRY(cudaFree(w.ptr));
+      w.ptr = nullptr;
+      w.bytes = 0;
+    }
+    const size_t want = std::max(bytes, static_cast<size_t>(1) << 20);
+    CUDA_TRY(cudaMalloc(&w.ptr, want));
+    w.bytes = want;
+  }
+  *out = static_cast<uint8_t*>(w.ptr);
+  return 0;
+}
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// ---- tensor maps --------------------------------------------------------------
+
+// 2-D byte tensor: `inner` contiguous bytes per row, `outer` rows `pitch` bytes
+// apart; 128-byte swizzled boxes of box_outer rows; out-of-range reads are zero.
+int make_tensor_map(CUtensorMap* tm, const void* base, uint64_t inner, uint64_t outer,
+                    uint64_t pitch, uint32_t box_outer) {
+  const cuuint64_t dims[2] = {inner, outer};
+  if (outer <= 1) pitch = (inner + 15) / 16 * 16;  // a single row: the pitch is never used
+  const cuuint64_t strides[1] = {pitch};
+  const cuuint32_t box[2] = {128, box_outer};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r =
+      g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with %d (base %p inner %llu outer %llu pitch %llu box %u)",
+              static_cast<int>(r), base, (unsigned long long)inner, (unsigned long long)outer,
+              (unsigned long long)pitch, box_outer);
+    return CPUOPS_B200_STATUS_CUDA_ERROR;
+  }
+  return 0;
+}
+
+bool tma_addressable(const void* base, int64_t pitch_bytes, int64_t outer) {
+  if (reinterpret_cast<uintptr_t>(base) & 15u) return false;
+  if (outer > 1 && (pitch_bytes & 15)) return false;
+  return true;
+}
+
+// ---- memory space ---------------------------------------------------------------
+
+bool is_device_pointer(const void* p, int memory_space) {
+  if (memory_space == CPUOPS_B200_MEM_DEVICE) return true;
+  if (memory_space == CPUOPS_B200_MEM_HOST) return false;
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+}
+
+// One matrix operand as the kernels see it.
+struct Matrix {
+  const uint8_t* ptr = nullptr;  // device
+  int64_t pitch = 0;             // bytes between consecutive "rows" (outer index)
+  int64_t inner_bytes = 0;       // valid bytes per row
+  int64_t outer = 0;             // number of rows
+};
+
+// Everything a call needs from the workspace, planned first, carved after.
+struct Plan {
+  size_t total = 0;
+  size_t take(size_t bytes) {
+    const size_t off = total;
+    total = align_up(total + bytes, 256);
+    return off;
+  }
+};
+
+struct Choice {
+  bool swap = false;
+  int BN = 128;
+  int nacc = 2;
+  int slices = 1;
+  int stages = 4;
+};
+
+int pick_bn_for_small(int nk) {
+  if (nk <= 32) return 32;
+  if (nk <= 64) return 64;
+  if (nk <= 128) return 128;
+  return 256;
+}
+
+// Cost of one configuration in MMA-pipe cycles (relative): waves of tiles over
+// the SMs times the per-tile time, where a k-block costs the larger of the MMA
+// issue time (BN/2 cycles for 128 x BN x 32 B) and the shared-memory read time
+// ((128 + BN) * 32 B at 128 B/clk); a single accumulator buffer cannot overlap
+// the epilogue with the next mainloop.
+double config_cost(int Mk, int Nk, int k_blocks, int BN, int nacc, int sms, bool beta) {
+  const int64_t tiles = static_cast<int64_t>((Mk + 127) / 128) * ((Nk + BN - 1) / BN);
+  const int64_t waves = (tiles + sms - 1) / sms;
+  const double kblock = 4.0 * std::max(BN / 2.0, (128.0 + BN) / 4.0);
+  const double epi = 128.0 * BN * (beta ? 8.0 : 4.0) / 20.0;  // ~20 B/clk/SM of HBM
+  const double tile = k_blocks * kblock + (nacc == 1 ? epi : 0.15 * epi);
+  return static_cast<double>(waves) * tile;
+}
+
+}  // namespace
+
+// =================================================================================
+
+extern "C" {
+
+CPUOPS_B200_API int cpuops_b200_abi_version(void) { return CPUOPS_B200_ABI_VERSION; }
+
+CPUOPS_B200_API const char* cpuops_b200_last_error(void) { return g_last_error; }
+
+CPUOPS_B200_API uint64_t cpuops_b200_launch_count(void) { return g_launches.load(); }
+
+CPUOPS_B200_API int cpuops_b200_device_count(void) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  return probe_devices();
+}
+
+CPUOPS_B200_API int cpuops_b200_shard_rows(int32_t m, int32_t world, int32_t rank,
+                                           int32_t* row_begin, int32_t* row_count) {
+  if (m < 0 || world < 1 || rank < 0 || rank >= world || !row_begin || !row_count)
+    return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+  // balanced contiguous split of the 128-row tiles, remainder to the first ranks
+  const int tiles = (m + kTileM - 1) / kTileM;
+  const int base = tiles / world, rem = tiles % world;
+  const int t0 = rank * base + std::min(rank, rem);
+  const int tn = base + (rank < rem ? 1 : 0);
+  const int r0 = std::min(m, t0 * kTileM);
+  const int r1 = std::min(m, (t0 + tn) * kTileM);
+  *row_begin = r0;
+  *row_count = r1 - r0;
+  return 0;
+}
+
+CPUOPS_B200_API size_t cpuops_b200_scale_layout_bytes(int32_t rows, int32_t k, int32_t tile_rows,
+                                                      int32_t blocks_per_stage) {
+  if (rows <= 0 || k <= 0 || tile_rows <= 0 || (blocks_per_stage != 4 && blocks_per_stage != 8))
+    return 0;
+  const int64_t tiles = (rows + tile_rows - 1) / tile_rows;
+  const int64_t stages = (static_cast<int64_t>(k) + blocks_per_stage * 32 - 1) / (blocks_per_stage * 32);
+  const int64_t nb128 = (tile_rows + 127) / 128;
+  return static_cast<size_t>(tiles * stages * (blocks_per_stage / 4) * nb128 * 512);
+}
+
+static int launch_relayout(const void* scales, int rows, int k, int ld, int tile_rows, int bps,
+                           void* out, cudaStream_t stream) {
+  ScaleLayout L;
+  L.rows = rows;
+  L.kblocks = (k + 31) / 32;
+  L.ld = ld;
+  L.tile_rows = tile_rows;
+  L.nb128 = (tile_rows + 127) / 128;
+  L.bps = bps;
+  L.ka = bps / 4;
+  L.tiles = (rows + tile_rows - 1) / tile_rows;
+  L.stages = (k + bps * 32 - 1) / (bps * 32);
+  const int64_t atoms = static_cast<int64_t>(L.tiles) * L.stages * L.ka * L.nb128;
+  const int threads = 256;
+  const int64_t blocks = std::min<int64_t>((atoms * 32 + threads - 1) / threads, 148 * 16);
+  relayout_scales_kernel<<<static_cast<unsigned>(std::max<int64_t>(blocks, 1)), threads, 0, stream>>>(
+      static_cast<const uint8_t*>(scales), static_cast<uint8_t*>(out), L);
+  g_launches.fetch_add(1);
+  CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+CPUOPS_B200_API int cpuops_b200_relayout_scales(const void* scales, int32_t rows, int32_t k,
+                                                int32_t ld_scales, int32_t tile_rows,
+                                                int32_t blocks_per_stage, void* out, void* stream) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!scales || !out || rows <= 0 || k <= 0 || ld_scales < (k + 31) / 32 || tile_rows <= 0 ||
+      tile_rows % 32 != 0 || (blocks_per_stage != 4 && blocks_per_stage != 8)) {
+    set_error("relayout_scales: invalid arguments");
+    return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+  }
+  DeviceState* st = nullptr;
+  if (int rc = init_device(-1, &st)) return rc;
+  cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : st->stream;
+  if (int rc = launch_relayout(scales, rows, k, ld_scales, tile_rows, blocks_per_stage, out, s))
+    return rc;
+  if (!stream) CUDA_TRY(cudaStreamSynchronize(s));
+  return 0;
+}
+
+CPUOPS_B200_API int cpuops_b200_stream_status(void* stream) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceState* st = nullptr;
+  if (int rc = init_device(-1, &st)) return rc;
+  cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : st->stream;
+  CUDA_TRY(cudaMemcpyAsync(st->error_host, st->error_dev, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+  CUDA_TRY(cudaStreamSynchronize(s));
+  if (*st->error_host != 0) {
+    set_error("device-side bounded wait timed out (code %d)", *st->error_host);
+    *st->error_host = 0;
+    CUDA_TRY(cudaMemsetAsync(st->error_dev, 0, sizeof(int32_t), s));
+    CUDA_TRY(cudaStreamSynchronize(s));
+    return CPUOPS_B200_STATUS_DEVICE_TIMEOUT;
+  }
+  return 0;
+}
+
+CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
+  if (!d || d->struct_size != sizeof(cpuops_b200_gemm_desc)) {
+    set_error("descriptor is null or struct_size does not match this library (ABI %d)",
+              CPUOPS_B200_ABI_VERSION);
+    return CPUOPS_B200_STATUS_BAD_DESCRIPTOR;
+  }
+  const bool is_mx = d->kind == CPUOPS_B200_KIND_MX;
+  if (d->kind != CPUOPS_B200_KIND_I8 && !is_mx) {
+    set_error("unknown kind %d", d->kind);
+    return CPUOPS_B200_STATUS_BAD_DESCRIPTOR;
+  }
+  if (is_mx) {
+    auto ok_fmt = [](int f) { return f == CPUOPS_B200_FMT_E4M3 || f == CPUOPS_B200_FMT_E5M2 || f == CPUOPS_B200_FMT_E2M1; };
+    if (!ok_fmt(d->a_format) || !ok_fmt(d->b_format)) {
+      set_error("MX operands must be e4m3, e5m2 or e2m1");
+      return CPUOPS_B200_STATUS_BAD_DESCRIPTOR;
+    }
+  } else if (d->a_format != CPUOPS_B200_FMT_U8 || d->b_format != CPUOPS_B200_FMT_S8) {
+    set_error("the int8 path is u8 x s8 -> s32");
+    return CPUOPS_B200_STATUS_BAD_DESCRIPTOR;
+  }
+  if (d->n_ops < 0 || d->n_ops > CPUOPS_B200_MAX_OPS) {
+    set_error("n_ops out of range");
+    return CPUOPS_B200_STATUS_BAD_DESCRIPTOR;
+  }
+
+  // ---- validation, in the CPU library's order (gemm.h:100-122, gemm_mx.h:79-112) ----
+  const int m = d->m, n = d->n, k = d->k;
+  if (m < 0 || n < 0 || k < 0) return CPUOPS_B200_STATUS_INVALID_PROBLEM;
+  if (m == 0 || n == 0) return CPUOPS_B200_STATUS_SUCCESS;
+  const bool c_rm = d->c_row_major != 0;
+  const bool fp4_a = is_mx && d->a_format == CPUOPS_B200_FMT_E2M1;
+  const bool fp4_b = is_mx && d->b_format == CPUOPS_B200_FMT_E2M1;
+  if (k > 0) {
+    if (!d->a || !d->b || !d->c || !d->d || (is_mx && (!d->a_scales || !d->b_scales)))
+      return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+    if (is_mx) {
+      const int sld = (k + 31) / 32;
+      if (d->lda < k || d->ldb < k || d->ld_scales_a < sld || d->ld_scales_b < sld)
+        return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+      if ((fp4_a && (d->lda & 1)) || (fp4_b && (d->ldb & 1))) return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+    } else {
+      if (d->lda < (d->a_row_major ? k : m) || d->ldb < (d->b_row_major ? n : k))
+        return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+    }
+    if (d->ldc < (c_rm ? n : m) || d->ldd < (c_rm ? n : m)) return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+  } else {
+    // k == 0 runs the epilogue over C before any pointer / ld check of A and B
+    // (gemm.h:106-110); C and D themselves are dereferenced, so they must exist.
+    if (!d->c || !d->d) return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+  }
+  if (is_mx && (fp4_a != fp4_b)) {
+    set_error("mixing fp4 with fp8 operands is not built yet");
+    return CPUOPS_B200_STATUS_UNSUPPORTED;
+  }
+  for (int t = 0; t < d->n_ops; ++t) {
+    const int oc = d->ops[t].opcode;
+    if (oc < CPUOPS_B200_OP_RELU || oc > CPUOPS_B200_OP_SILU) {
+      set_error("unknown epilogue opcode %d", oc);
+      return CPUOPS_B200_STATUS_BAD_DESCRIPTOR;
+    }
+    if (!is_mx && (oc == CPUOPS_B200_OP_GELU || oc == CPUOPS_B200_OP_SILU)) {
+      set_error("Gelu/Silu are defined for f32 accumulators only");
+      return CPUOPS_B200_STATUS_UNSUPPORTED;
+    }
+    if ((oc == CPUOPS_B200_OP_BIAS_ADD || oc == CPUOPS_B200_OP_SCALE_PER_ROW ||
+         oc == CPUOPS_B200_OP_SCALE_PER_COL) && !d->ops[t].ptr)
+      return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+  }
+
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceState* stp = nullptr;
+  if (int rc = init_device(d->device, &stp)) return rc;
+  DeviceState& st = *stp;
+  cudaStream_t stream = d->stream ? static_cast<cudaStream_t>(d->stream) : st.stream;
+  const bool async = (d->flags & CPUOPS_B200_FLAG_ASYNC) != 0;
+
+  // ---- which pointers are host memory -------------------------------------------
+  const bool a_dev = k == 0 || is_device_pointer(d->a, d->memory_space);
+  const bool b_dev = k == 0 || is_device_pointer(d->b, d->memory_space);
+  const bool sa_dev = !is_mx || k == 0 || is_device_pointer(d->a_scales, d->memory_space);
+  const bool sb_dev = !is_mx || k == 0 || is_device_pointer(d->b_scales, d->memory_space);
+  const bool beta_nonzero = is_mx ? (d->beta.f32 != 0.0f) : (d->beta.i32 != 0);
+  const bool c_dev = is_device_pointer(d->c, d->memory_space);
+  const bool d_dev = is_device_pointer(d->d, d->memory_space);
+  bool op_dev[CPUOPS_B200_MAX_OPS];
+  for (int t = 0; t < d->n_ops; ++t)
+    op_dev[t] = !d->ops[t].ptr || is_device_pointer(d->ops[t].ptr, d->memory_space);
+  const bool any_host = !(a_dev && b_dev && sa_dev && sb_dev && c_dev && d_dev) ||
+                        std::any_of(op_dev, op_dev + d->n_ops, [](bool x) { return !x; });
+  if (async && any_host) {
+    set_error("FLAG_ASYNC needs every operand in device memory");
+    return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+  }
+
+  // ---- operand geometry (bytes) ----------------------------------------------------
+  // A-side: rows of the caller's storage.  int8 row-major A: m rows of k bytes; column-major A:
+  // k rows of m bytes (m contiguous).  B likewise (row-major B: k rows of n bytes).  MX: both are
+  // rows of k elements (fp4: k/2 bytes, rounded up).
+  const bool a_kmajor = is_mx || d->a_row_major;   // k contiguous
+  const bool b_kmajor = is_mx || !d->b_row_major;
+  auto row_bytes = [&](bool fp4, int elems) -> int64_t { return fp4 ? (elems + 1) / 2 : elems; };
+  Matrix A, B;
+  A.outer = a_kmajor ? m : k;
+  A.inner_bytes = a_kmajor ? row_bytes(fp4_a, k) : m;
+  A.pitch = fp4_a ? d->lda / 2 : d->lda;
+  B.outer = b_kmajor ? n : k;
+  B.inner_bytes = b_kmajor ? row_bytes(fp4_b, k) : n;
+  B.pitch = fp4_b ? d->ldb / 2 : d->ldb;
+
+  // ---- configuration -----------------------------------------------------------------
+  Choice ch;
+  const int elems_per_block = (fp4_a ? 256 : 128);  // k elements per 128-byte stage row
+  const int k_blocks = k > 0 ? (k + elems_per_block - 1) / elems_per_block : 0;
+  const int kind = !is_mx ? kKindI8 : (fp4_a ? kKindMxf4 : kKindMxf8);
+  if (k > 0) {
+    ch.swap = (m <= 64 && n > m);
+    const int Mk = ch.swap ? n : m, Nk = ch.swap ? m : n;
+    const bool bk_role_mn = !(ch.swap ? a_kmajor : b_kmajor);  // N-side operand is MN-major
+    if (d->tile_n > 0) {
+      ch.BN = d->tile_n;
+    } else if (Nk <= 128) {
+      ch.BN = bk_role_mn ? 128 : pick_bn_for_small(Nk);
+    } else {
+      double best = 1e300;
+      for (int bn : {256, 192, 128}) {
+        if (bk_role_mn && bn == 192) continue;
+        const int nacc = (is_mx && bn == 256) ? 1 : 2;
+        const double c = config_cost(Mk, Nk, k_blocks, bn, nacc, st.sm_count, beta_nonzero);
+        if (c < best) {
+          best = c;
+          ch.BN = bn;
+        }
+      }
+    }
+    if (ch.BN % 32 != 0 || ch.BN < 32 || ch.BN > 256 || (bk_role_mn && ch.BN % 128 != 0)) {
+      set_error("tile_n %d is not usable here", ch.BN);
+      return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+    }
+    ch.nacc = (is_mx && ch.BN > 224) ? 1 : 2;
+    const int64_t tiles = static_cast<int64_t>((Mk + 127) / 128) * ((Nk + ch.BN - 1) / ch.BN);
+    if (d->split_k_slices > 1) {
+      ch.slices = std::min(d->split_k_slices, k_blocks);
+    } else if (d->split_k_slices == 0 && tiles < 2 * st.sm_count && k_blocks >= 8) {
+      // Few tiles and a deep k: cut k so that the work items fill the SMs.  Time
+      // estimate (microseconds): waves x k-blocks per slice x per-block time, plus
+      // the slab write + read and one more launch when split.
+      const double hbm_bytes_per_us = 6.0e6, per_sm = hbm_bytes_per_us / st.sm_count;
+      const double block_us = std::max(gemm_stage_bytes(ch.BN) / per_sm,
+                                       4.0 * std::max(ch.BN / 2.0, (128.0 + ch.BN) / 4.0) / 1500.0);
+      double best = 1e300;
+      for (int s = 1; s <= std::min(32, k_blocks / 2); ++s) {
+        const int64_t waves = (tiles * s + st.sm_count - 1) / st.sm_count;
+        const int per_slice = (k_blocks + s - 1) / s;
+        double t_us = static_cast<double>(waves) * per_slice * block_us;
+        if (s > 1) t_us += 2.0 * s * Mk * static_cast<double>(Nk) * 4.0 / hbm_bytes_per_us + 3.0;
+        if (t_us < best * 0.97) {
+          best = t_us;
+          ch.slices = s;
+        }
+      }
+    }
+  }
+
+  // ---- workspace plan ------------------------------------------------------------------
+  Plan plan;
+  const int64_t c_outer = c_rm ? m : n, c_inner = c_rm ? n : m;
+  size_t off_a = 0, off_b = 0, off_sa = 0, off_sb = 0, off_c = 0, off_d = 0, off_sfa = 0, off_sfb = 0,
+         off_ws = 0, off_ops[CPUOPS_B200_MAX_OPS] = {0};
+  int64_t a_pitch_dev = A.pitch, b_pitch_dev = B.pitch;
+  bool a_repack = false, b_repack = false;
+  const bool a_mask = fp4_a && (k & 1), b_mask = fp4_b && (k & 1);
+  if (k > 0) {
+    if (!a_dev) {
+      a_pitch_dev = align_up(A.inner_bytes, 16);
+      off_a = plan.take(a_pitch_dev * A.outer);
+    } else if (!tma_addressable(d->a, A.pitch, A.outer) || a_mask) {
+      a_repack = true;
+      a_pitch_dev = align_up(A.inner_bytes, 16);
+      off_a = plan.take(a_pitch_dev * A.outer);
+    }
+    if (!b_dev) {
+      b_pitch_dev = align_up(B.inner_bytes, 16);
+      off_b = plan.take(b_pitch_dev * B.outer);
+    } else if (!tma_addressable(d->b, B.pitch, B.outer) || b_mask) {
+      b_repack = true;
+      b_pitch_dev = align_up(B.inner_bytes, 16);
+      off_b = plan.take(b_pitch_dev * B.outer);
+    }
+    if (is_mx) {
+      if (!sa_dev) off_sa = plan.take(static_cast<size_t>(m) * d->ld_scales_a);
+      if (!sb_dev) off_sb = plan.take(static_cast<size_t>(n) * d->ld_scales_b);
+    }
+  }
+  const bool stage_c = !c_dev && beta_nonzero;
+  int64_t c_ld_dev = d->ldc, d_ld_dev = d->ldd;
+  if (stage_c) {
+    c_ld_dev = align_up(c_inner, 4);
+    off_c = plan.take(static_cast<size_t>(c_ld_dev) * c_outer * 4);
+  }
+  if (!d_dev) {
+    d_ld_dev = align_up(c_inner, 4);
+    off_d = plan.take(static_cast<size_t>(d_ld_dev) * c_outer * 4);
+  }
+  for (int t = 0; t < d->n_ops; ++t) {
+    if (!op_dev[t]) {
+      const int oc = d->ops[t].opcode;
+      const size_t len = (oc == CPUOPS_B200_OP_SCALE_PER_ROW) ? m : n;
+      off_ops[t] = plan.take(len * 4);
+    }
+  }
+  int Mk = 0, Nk = 0, bps = 0;
+  size_t sfa_bytes = 0, sfb_bytes = 0;
+  if (k > 0) {
+    Mk = ch.swap ? n : m;
+    Nk = ch.swap ? m : n;
+    if (is_mx) {
+      bps = fp4_a ? 8 : 4;
+      sfa_bytes = cpuops_b200_scale_layout_bytes(Mk, k, kTileM, bps);
+      sfb_bytes = cpuops_b200_scale_layout_bytes(Nk, k, ch.BN, bps);
+      off_sfa = plan.take(sfa_bytes);
+      off_sfb = plan.take(sfb_bytes);
+    }
+    if (ch.slices > 1) off_ws = plan.take(static_cast<size_t>(ch.slices) * Mk * Nk * 4);
+  }
+  uint8_t* wsp = nullptr;
+  if (plan.total > 0) {
+    if (int rc = ensure_workspace(st, stream, plan.total, &wsp)) return rc;
+  }
+
+  // ---- stage host operands -------------------------------------------------------------
+  const uint8_t* a_ptr = static_cast<const uint8_t*>(d->a);
+  const uint8_t* b_ptr = static_cast<const uint8_t*>(d->b);
+  const uint8_t* sa_ptr = static_cast<const uint8_t*>(d->a_scales);
+  const uint8_t* sb_ptr = static_cast<const uint8_t*>(d->b_scales);
+  const uint8_t* c_ptr = static_cast<const uint8_t*>(d->c);
+  uint8_t* d_ptr = static_cast<uint8_t*>(d->d);
+  if (k > 0) {
+    if (!a_dev) {
+      CUDA_TRY(cudaMemcpy2DAsync(wsp + off_a, a_pitch_dev, d->a, A.pitch, A.inner_bytes, A.outer,
+                                 cudaMemcpyHostToDevice, stream));
+      a_ptr = wsp + off_a;
+      if (a_mask) {  // clear the out-of-range nibble of an odd-k fp4 row in place
+        repack_rows_kernel<<<std::min<int64_t>((A.outer * ((A.inner_bytes + 15) / 16) + 255) / 256, 2368),
+                             256, 0, stream>>>(a_ptr, a_pitch_dev, wsp + off_a, a_pitch_dev,
+                                               static_cast<int>(A.outer),
+                                               static_cast<int>(A.inner_bytes), 1);
+        g_launches.fetch_add(1);
+      }
+    } else if (a_repack) {
+      repack_rows_kernel<<<static_cast<unsigned>(std::min<int64_t>(
+                               (A.outer * ((A.inner_bytes + 15) / 16) + 255) / 256, 2368)),
+                           256, 0, stream>>>(a_ptr, A.pitch, wsp + off_a, a_pitch_dev,
+                                             static_cast<int>(A.outer),
+                                             static_cast<int>(A.inner_bytes), a_mask ? 1 : 0);
+      g_launches.fetch_add(1);
+      a_ptr = wsp + off_a;
+    }
+    if (!b_dev) {
+      CUDA_TRY(cudaMemcpy2DAsync(wsp + off_b, b_pitch_dev, d->b, B.pitch, B.inner_bytes, B.outer,
+                                 cudaMemcpyHostToDevice, stream));
+      b_ptr = wsp + off_b;
+      if (b_mask) {
+        repack_rows_kernel<<<std::min<int64_t>((B.outer * ((B.inner_bytes + 15) / 16) + 255) / 256, 2368),
+                             256, 0, stream>>>(b_ptr, b_pitch_dev, wsp + off_b, b_pitch_dev,
+                                               static_cast<int>(B.outer),
+                                               static_cast<int>(B.inner_bytes), 1);
+        g_launches.fetch_add(1);
+      }
+    } else if (b_repack) {
+      repack_rows_kernel<<<static_cast<unsigned>(std::min<int64_t>(
+                               (B.outer * ((B.inner_bytes + 15) / 16) + 255) / 256, 2368)),
+                           256, 0, stream>>>(b_ptr, B.pitch, wsp + off_b, b_pitch_dev,
+                                             static_cast<int>(B.outer),
+                                             static_cast<int>(B.inner_bytes), b_mask ? 1 : 0);
+      g_launches.fetch_add(1);
+      b_ptr = wsp + off_b;
+    }
+    if (is_mx && !sa_dev) {
+      CUDA_TRY(cudaMemcpyAsync(wsp + off_sa, d->a_scales, static_cast<size_t>(m - 1) * d->ld_scales_a + (k + 31) / 32,
+                               cudaMemcpyHostToDevice, stream));
+      sa_ptr = wsp + off_sa;
+    }
+    if (is_mx && !sb_dev) {
+      CUDA_TRY(cudaMemcpyAsync(wsp + off_sb, d->b_scales, static_cast<size_t>(n - 1) * d->ld_scales_b + (k + 31) / 32,
+                               cudaMemcpyHostToDevice, stream));
+      sb_ptr = wsp + off_sb;
+    }
+  }
+  if (stage_c) {
+    CUDA_TRY(cudaMemcpy2DAsync(wsp + off_c, c_ld_dev * 4, d->c, static_cast<size_t>(d->ldc) * 4,
+                               c_inner * 4, c_outer, cudaMemcpyHostToDevice, stream));
+    c_ptr = wsp + off_c;
+  } else if (!c_dev) {
+    c_ptr = wsp;  // never dereferenced (beta == 0)
+  }
+  if (!d_dev) d_ptr = wsp + off_d;
+
+  // ---- epilogue parameters in kernel view ------------------------------------------------
+  EpilogueParams epi;
+  memset(&epi, 0, sizeof(epi));
+  const bool swap = ch.swap;
+  // caller element (i, j): offset i*ld + j (row-major) or j*ld + i (column-major);
+  // kernel row = swap ? j : i, kernel col = swap ? i : j.
+  const int64_t d_si = c_rm ? d_ld_dev : 1, d_sj = c_rm ? 1 : d_ld_dev;
+  const int64_t c_si = c_rm ? c_ld_dev : 1, c_sj = c_rm ? 1 : c_ld_dev;
+  epi.D = d_ptr;
+  epi.C = c_ptr;
+  epi.d_sr = swap ? d_sj : d_si;
+  epi.d_sc = swap ? d_si : d_sj;
+  epi.c_sr = swap ? c_sj : c_si;
+  epi.c_sc = swap ? c_si : c_sj;
+  memcpy(&epi.alpha, &d->alpha, 4);
+  memcpy(&epi.beta, &d->beta, 4);
+  epi.beta_nonzero = beta_nonzero ? 1 : 0;
+  epi.activation = d->activation == CPUOPS_B200_ACT_RELU ? 1 : 0;
+  epi.n_ops = d->n_ops;
+  for (int t = 0; t < d->n_ops; ++t) {
+    const cpuops_b200_epilogue_op& op = d->ops[t];
+    EpilogueOp& o = epi.ops[t];
+    o.opcode = op.opcode;
+    const bool by_user_row = op.opcode == CPUOPS_B200_OP_SCALE_PER_ROW;
+    o.index_by_krow = (by_user_row != swap) ? 1 : 0;
+    o.ptr = op.ptr;
+    if (op.ptr && !op_dev[t]) {
+      const size_t len = by_user_row ? m : n;
+      CUDA_TRY(cudaMemcpyAsync(wsp + off_ops[t], op.ptr, len * 4, cudaMemcpyHostToDevice, stream));
+      o.ptr = wsp + off_ops[t];
+    }
+    memcpy(&o.lo, &op.lo, 4);
+    memcpy(&o.hi, &op.hi, 4);
+  }
+
+  const int ew_threads = 256;
+  auto ew_blocks = [&](int64_t total) {
+    return static_cast<unsigned>(std::max<int64_t>(
+        1, std::min<int64_t>((total + ew_threads - 1) / ew_threads, static_cast<int64_t>(st.sm_count) * 16)));
+  };
+
+  if (k == 0) {
+    // D = epilogue(0, C): run_blocked.h:30-36.  Kernel view == caller view here.
+    const int64_t sr = c_rm ? 1 : 0;  // compact order follows D's contiguous direction
+    if (is_mx) {
+      reduce_epilogue_kernel<false><<<ew_blocks(static_cast<int64_t>(m) * n), ew_threads, 0, stream>>>(
+          epi, nullptr, 0, 0, m, n, sr ? n : 1, sr ? 1 : m);
+    } else {
+      reduce_epilogue_kernel<true><<<ew_blocks(static_cast<int64_t>(m) * n), ew_threads, 0, stream>>>(
+          epi, nullptr, 0, 0, m, n, sr ? n : 1, sr ? 1 : m);
+    }
+    g_launches.fetch_add(1);
+    CUDA_TRY(cudaGetLastError());
+  } else {
+    // ---- scales -> tile-ordered layout (MX) ------------------------------------------------
+    const uint8_t* ak_ptr = swap ? b_ptr : a_ptr;  // kernel-view A (M side), B (N side)
+    const uint8_t* bk_ptr = swap ? a_ptr : b_ptr;
+    const Matrix& AkM = swap ? B : A;
+    const Matrix& BkM = swap ? A : B;
+    const int64_t ak_pitch = swap ? b_pitch_dev : a_pitch_dev;
+    const int64_t bk_pitch = swap ? a_pitch_dev : b_pitch_dev;
+    const bool ak_kmajor = swap ? b_kmajor : a_kmajor;
+    const bool bk_kmajor = swap ? a_kmajor : b_kmajor;
+    if (is_mx) {
+      const uint8_t* sak = swap ? sb_ptr : sa_ptr;
+      const uint8_t* sbk = swap ? sa_ptr : sb_ptr;
+      const int ldsak = swap ? d->ld_scales_b : d->ld_scales_a;
+      const int ldsbk = swap ? d->ld_scales_a : d->ld_scales_b;
+      if (int rc = launch_relayout(sak, Mk, k, ldsak, kTileM, bps, wsp + off_sfa, stream)) return rc;
+      if (int rc = launch_relayout(sbk, Nk, k, ldsbk, ch.BN, bps, wsp + off_sfb, stream)) return rc;
+    }
+
+    // ---- tensor maps -----------------------------------------------------------------------
+    CUtensorMap tmA, tmB;
+    if (int rc = make_tensor_map(&tmA, ak_ptr, AkM.inner_bytes, AkM.outer, ak_pitch, 128)) return rc;
+    if (int rc = make_tensor_map(&tmB, bk_ptr, BkM.inner_bytes, BkM.outer, bk_pitch,
+                                 bk_kmajor ? static_cast<uint32_t>(ch.BN) : 128u))
+      return rc;
+
+    GemmParams p;
+    memset(&p, 0, sizeof(p));
+    p.Mk = Mk;
+    p.Nk = Nk;
+    p.K = k;
+    p.m_tiles = (Mk + kTileM - 1) / kTileM;
+    p.n_tiles = (Nk + ch.BN - 1) / ch.BN;
+    p.k_blocks = k_blocks;
+    p.slices = ch.slices;
+    p.BN = ch.BN;
+    p.nacc = ch.nacc;
+    p.a_mn_major = ak_kmajor ? 0 : 1;
+    p.b_mn_major = bk_kmajor ? 0 : 1;
+    if (!is_mx) {
+      // A side is u8 unless the operands were swapped (then it is the caller's s8 B)
+      const uint32_t a_fmt = swap ? 1u : 0u, b_fmt = swap ? 0u : 1u;
+      p.idesc = make_idesc(2 /*s32*/, a_fmt, b_fmt, p.a_mn_major, p.b_mn_major, kTileM, ch.BN);
+    } else if (kind == kKindMxf8) {
+      const int fa = swap ? d->b_format : d->a_format, fb = swap ? d->a_format : d->b_format;
+      p.idesc = make_idesc_block_scaled(fa == CPUOPS_B200_FMT_E5M2 ? 1u : 0u,
+                                        fb == CPUOPS_B200_FMT_E5M2 ? 1u : 0u, kTileM, ch.BN);
+    } else {
+      p.idesc = make_idesc_block_scaled(1u, 1u, kTileM, ch.BN);  // e2m1 x e2m1
+    }
+    p.mode = ch.slices > 1 ? kModePartial : kModeEpilogue;
+    p.epi = epi;
+    if (ch.slices > 1) {
+      p.ws = wsp + off_ws;
+      p.ws_slab = static_cast<int64_t>(Mk) * Nk;
+      // compact slab order follows D's contiguous direction in kernel view
+      if (epi.d_sr == 1) {
+        p.ws_sr = 1;
+        p.ws_sc = Mk;
+      } else {
+        p.ws_sr = Nk;
+        p.ws_sc = 1;
+      }
+    }
+    if (is_mx) {
+      p.sfa = wsp + off_sfa;
+      p.sfb = wsp + off_sfb;
+      p.sfa_stage_bytes = (bps / 4) * 512;
+      p.sfb_stage_bytes = (bps / 4) * ((ch.BN + 127) / 128) * 512;
+      const int sf_cols = (p.sfa_stage_bytes + p.sfb_stage_bytes) / 512 * 4;
+      if (ch.nacc * ch.BN + sf_cols > 512) {
+        set_error("internal: tensor memory over-committed (BN %d)", ch.BN);
+        return CPUOPS_B200_STATUS_CUDA_ERROR;
+      }
+    }
+    p.error = st.error_dev;
+    const int per_stage = gemm_stage_bytes(ch.BN) + p.sfa_stage_bytes + p.sfb_stage_bytes;
+    int stages = (st.smem_optin - 1024 - 256) / per_stage;
+    stages = std::min({stages, kMaxStages, std::max(2, k_blocks)});
+    if (stages < 2) {
+      set_error("internal: shared memory too small for two stages");
+      return CPUOPS_B200_STATUS_CUDA_ERROR;
+    }
+    p.stages = stages;
+    // At least 120 KB so that two CTAs never share an SM: each allocates all of tensor memory.
+    const int smem = std::max(gemm_smem_bytes(ch.BN, stages, p.sfa_stage_bytes, p.sfb_stage_bytes),
+                              120 * 1024);
+    const int64_t total_tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles * p.slices;
+    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(total_tiles, st.sm_count));
+    if (kind == kKindI8) {
+      gemm_tcgen05_kernel<kKindI8><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, p);
+    } else if (kind == kKindMxf8) {
+      gemm_tcgen05_kernel<kKindMxf8><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, p);
+    } else {
+      gemm_tcgen05_kernel<kKindMxf4><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, p);
+    }
+    g_launches.fetch_add(1);
+    CUDA_TRY(cudaGetLastError());
+    if (ch.slices > 1) {
+      const int64_t total = static_cast<int64_t>(Mk) * Nk;
+      if (is_mx) {
+        reduce_epilogue_kernel<false><<<ew_blocks(total), ew_threads, 0, stream>>>(
+            epi, static_cast<const uint32_t*>(p.ws), ch.slices, p.ws_slab, Mk, Nk, p.ws_sr, p.ws_sc);
+      } else {
+        reduce_epilogue_kernel<true><<<ew_blocks(total), ew_threads, 0, stream>>>(
+            epi, static_cast<const uint32_t*>(p.ws), ch.slices, p.ws_slab, Mk, Nk, p.ws_sr, p.ws_sc);
+      }
+      g_launches.fetch_add(1);
+      CUDA_TRY(cudaGetLastError());
+    }
+  }
+
+  if (!d_dev) {
+    CUDA_TRY(cudaMemcpy2DAsync(d->d, static_cast<size_t>(d->ldd) * 4, d_ptr, d_ld_dev * 4, c_inner * 4,
+                               c_outer, cudaMemcpyDeviceToHost, stream));
+  }
+  if (async) return CPUOPS_B200_STATUS_SUCCESS;
+
+  CUDA_TRY(cudaMemcpyAsync(st.error_host, st.error_dev, sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+  CUDA_TRY(cudaStreamSynchronize(stream));
+  if (*st.error_host != 0) {
+    set_error("device-side bounded wait timed out (code %d)", *st.error_host);
+    *st.error_host = 0;
+    cudaMemsetAsync(st.error_dev, 0, sizeof(int32_t), stream);
+    cudaStreamSynchronize(stream);
+    return CPUOPS_B200_STATUS_DEVICE_TIMEOUT;
+  }
+  return CPUOPS_B200_STATUS_SUCCESS;
+}
+
+}  // extern "C"

@@ -1,0 +1,148 @@
+// Small HBM-bound helper kernels around the tensor-core GEMM:
+//   * relayout_scales_kernel  -- row-major E8M0 scales -> tile-ordered atoms
+//   * reduce_epilogue_kernel  -- split-k slab reduction in fixed slice order +
+//                                epilogue; with zero slabs it is the k == 0 path
+//   * repack_rows_kernel      -- copies an operand whose base / leading dimension
+//                                TMA cannot address into a 16-byte aligned pitch
+#pragma once
+
+#include "epilogue.cuh"
+#include "gemm_params.h"
+
+namespace b200 {
+
+// Scale layout consumed by tcgen05.cp (32x128b.warpx4) + block-scaled MMAs.
+// The CPU library reads scales[row*ld + kk/32] directly while packing
+// (gemm/threadblock/mma_policy_mx.h:213,219,242,248).  Here, for every tile of
+// `tile_rows` rows (128 on the MMA-M side, BN on the N side) and every pipeline
+// stage of `bps` scale blocks (4 for fp8: 128 elements, 8 for fp4: 256
+// elements), the stage chunk is an array of 512-byte atoms
+//     atom (ka, nb), ka < bps/4, nb < ceil(tile_rows/128)
+//     byte (r%32)*16 + ((r%128)/32)*4 + (kb%4)
+// for row r of the tile (nb = r/128) and scale block kb = stage*bps + ka*4 + kb%4.
+// One warp writes one atom (512 contiguous bytes); each lane gathers the 4x4
+// bytes of rows l, l+32, l+64, l+96.  Out-of-range rows / blocks get 127
+// (1.0): the zero-filled operand padding must never meet a NaN scale, and
+// caller memory past ceil(k/32) entries of a row is never read.
+struct ScaleLayout {
+  int rows, kblocks;       // valid rows, ceil(k/32)
+  int ld;                  // leading dimension of the source (entries)
+  int tile_rows, nb128;    // rows per tile, 128-row atoms per tile
+  int bps, ka;             // scale blocks per stage, atoms along k per stage
+  int tiles, stages;       // number of row tiles, pipeline stages along k
+};
+
+__global__ void relayout_scales_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                       ScaleLayout L) {
+  const int64_t atoms_total = static_cast<int64_t>(L.tiles) * L.stages * L.ka * L.nb128;
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const bool vec_ok = (L.ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(src) & 3u) == 0);
+  // Work order: consecutive warps walk k for a fixed 128-row group, so the
+  // 32-byte sectors of the source rows are reused out of L1/L2.
+  const int k_atoms = L.stages * L.ka;
+  for (int64_t w = warp0; w < atoms_total; w += nwarps) {
+    const int kq = static_cast<int>(w % k_atoms);             // atom index along k
+    const int64_t rg = w / k_atoms;                           // (tile, nb)
+    const int nb = static_cast<int>(rg % L.nb128);
+    const int tile = static_cast<int>(rg / L.nb128);
+    const int stage = kq / L.ka, ka = kq % L.ka;
+    const int kb0 = stage * L.bps + ka * 4;
+    uint32_t words[4];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const int r_in_tile = nb * 128 + g * 32 + lane;
+      const int row = tile * L.tile_rows + r_in_tile;
+      uint32_t word = 0x7F7F7F7Fu;
+      if (r_in_tile < L.tile_rows && row < L.rows && kb0 < L.kblocks) {
+        const uint8_t* s = src + static_cast<int64_t>(row) * L.ld + kb0;
+        if (vec_ok && kb0 + 3 < L.kblocks) {
+          word = *reinterpret_cast<const uint32_t*>(s);
+        } else {
+          word = 0;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t b = (kb0 + j < L.kblocks) ? s[j] : 127u;
+            word |= b << (8 * j);
+          }
+        }
+      }
+      words[g] = word;
+    }
+    const int64_t atom_off =
+        ((static_cast<int64_t>(tile) * L.stages + stage) * (L.ka * L.nb128) + ka * L.nb128 + nb) * 512;
+    *reinterpret_cast<uint4*>(dst + atom_off + lane * 16) =
+        make_uint4(words[0], words[1], words[2], words[3]);
+  }
+}
+
+// D = epilogue(sum_s slab_s) with the slabs added in slice order
+// ((w0 + w1) + w2) + ..., as the CPU library's reduce_splitk does
+// (gemm/kernel/run_blocked.h:40-75); slices == 0 is its write_zero_k (:30-36).
+// Threads walk the slab's compact order, which the launcher chooses to match
+// the contiguous direction of D.
+template <bool kInt>
+__global__ void reduce_epilogue_kernel(EpilogueParams e, const uint32_t* __restrict__ ws, int slices,
+                                       int64_t slab, int Mk, int Nk, int64_t ws_sr, int64_t ws_sc) {
+  const int64_t total = static_cast<int64_t>(Mk) * Nk;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += stride) {
+    int krow, kcol;
+    if (ws_sc == 1) {
+      krow = static_cast<int>(idx / Nk);
+      kcol = static_cast<int>(idx - static_cast<int64_t>(krow) * Nk);
+    } else {
+      kcol = static_cast<int>(idx / Mk);
+      krow = static_cast<int>(idx - static_cast<int64_t>(kcol) * Mk);
+    }
+    uint32_t acc = 0;
+    if (slices > 0) {
+      const uint32_t* w = ws + (krow * ws_sr + kcol * ws_sc);
+      acc = w[0];
+      for (int s = 1; s < slices; ++s) {
+        const uint32_t v = w[s * slab];
+        if constexpr (kInt) {
+          acc += v;
+        } else {
+          acc = __float_as_uint(__fadd_rn(__uint_as_float(acc), __uint_as_float(v)));
+        }
+      }
+    }
+    const uint32_t out = epilogue_element<kInt>(e, acc, krow, kcol);
+    static_cast<uint32_t*>(e.D)[krow * e.d_sr + kcol * e.d_sc] = out;
+  }
+}
+
+// Copies `rows` rows of `row_bytes` bytes (source pitch src_pitch, any
+// alignment) into a destination with a 16-byte aligned pitch.  When
+// `mask_last_high_nibble` is set the high nibble of each row's last byte is
+// cleared (packed fp4 with an odd k: that nibble belongs to element k, which is
+// outside the problem).  One thread per 16 destination bytes.
+__global__ void repack_rows_kernel(const uint8_t* __restrict__ src, int64_t src_pitch,
+                                   uint8_t* __restrict__ dst, int64_t dst_pitch, int rows,
+                                   int row_bytes, int mask_last_high_nibble) {
+  const int chunks_per_row = (row_bytes + 15) / 16;
+  const int64_t total = static_cast<int64_t>(rows) * chunks_per_row;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += stride) {
+    const int row = static_cast<int>(idx / chunks_per_row);
+    const int c0 = static_cast<int>(idx - static_cast<int64_t>(row) * chunks_per_row) * 16;
+    const uint8_t* s = src + row * src_pitch + c0;
+    uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      uint32_t b = 0;
+      if (c0 + j < row_bytes) {
+        b = s[j];
+        if (mask_last_high_nibble && c0 + j == row_bytes - 1) b &= 0x0Fu;
+      }
+      w[j >> 2] |= b << (8 * (j & 3));
+    }
+    *reinterpret_cast<uint4*>(dst + row * dst_pitch + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+}  // namespace b200

@@ -1,0 +1,87 @@
+// Kernel-side parameter blocks shared by the launcher (api.cu) and the kernels.
+//
+// "Kernel view": the tensor-core kernel always computes Dk (Mk x Nk) = Ak * Bk
+// with Ak on the MMA-M side (128-row tiles) and Bk on the MMA-N side (BN-column
+// tiles).  The launcher may swap the caller's operands (small-m problems put
+// the wide operand on the M side); the caller's row/column strides of C and D,
+// and whether a chain op indexes its vector by row or by column, are translated
+// into this view so the kernels never need to know.
+#pragma once
+
+#include <stdint.h>
+
+namespace b200 {
+
+constexpr int kTileM = 128;       // MMA M (one CTA, cta_group::1)
+constexpr int kStageRowBytes = 128;  // one 128-byte swizzle row of k per pipeline stage
+constexpr int kMaxOps = 8;
+constexpr int kMaxStages = 8;
+
+enum : int32_t { kKindI8 = 0, kKindMxf8 = 1, kKindMxf4 = 2 };
+enum : int32_t { kModeEpilogue = 0, kModePartial = 1 };
+enum : int32_t {
+  kOpRelu = 1, kOpClamp = 2, kOpBiasAdd = 3, kOpScalePerRow = 4, kOpScalePerCol = 5,
+  kOpGelu = 6, kOpSilu = 7
+};
+// Device error word values (first writer wins).
+enum : int32_t {
+  kErrNone = 0,
+  kErrProducerWait = 1,   // TMA producer gave up waiting for a free stage
+  kErrMmaWaitFull = 2,    // MMA issuer gave up waiting for a loaded stage
+  kErrMmaWaitAcc = 3,     // MMA issuer gave up waiting for a drained accumulator
+  kErrEpilogueWait = 4,   // epilogue gave up waiting for a finished accumulator
+  kErrDrainWait = 5       // teardown gave up waiting for in-flight work
+};
+
+struct EpilogueOp {
+  int32_t opcode;
+  int32_t index_by_krow;  // 1: vector indexed by the kernel-view row, 0: by column
+  const void* ptr;
+  uint32_t lo, hi;        // raw bits of s32 / f32 clamp bounds
+};
+
+// Everything the epilogue needs; shared by the GEMM kernel, the split-k reduce
+// kernel and the k == 0 kernel.
+struct EpilogueParams {
+  void* D;
+  const void* C;
+  int64_t d_sr, d_sc;     // element strides of D in kernel view (row, col)
+  int64_t c_sr, c_sc;
+  uint32_t alpha, beta;   // raw bits (s32 or f32)
+  int32_t beta_nonzero;
+  int32_t activation;     // 0 none, 1 relu
+  int32_t n_ops;
+  EpilogueOp ops[kMaxOps];
+};
+
+struct GemmParams {
+  int32_t Mk, Nk, K;        // kernel-view extents; K in elements
+  int32_t m_tiles, n_tiles;
+  int32_t k_blocks;         // 128-byte k blocks covering K
+  int32_t slices;           // split-k slices (>= 1, <= k_blocks)
+  int32_t BN;               // N tile (multiple of 32, <= 256)
+  int32_t stages;           // smem pipeline depth
+  int32_t nacc;             // TMEM accumulator buffers (1 or 2)
+  int32_t a_mn_major, b_mn_major;
+  uint32_t idesc;           // instruction descriptor without scale-factor ids
+  int32_t mode;             // kModeEpilogue | kModePartial
+  EpilogueParams epi;
+  // split-k slabs: element (s, krow, kcol) at ws[s*ws_slab + krow*ws_sr + kcol*ws_sc]
+  void* ws;
+  int64_t ws_slab, ws_sr, ws_sc;
+  // MX: re-laid-out scale factors, one contiguous chunk per (tile, stage)
+  const uint8_t* sfa;
+  const uint8_t* sfb;
+  int32_t sfa_stage_bytes, sfb_stage_bytes;
+  int32_t* error;           // device error word
+};
+
+// Shared-memory footprint of one launch of the GEMM kernel.
+__host__ __device__ inline int gemm_stage_bytes(int BN) { return kTileM * 128 + BN * 128; }
+__host__ __device__ inline int gemm_smem_bytes(int BN, int stages, int sfa_stage_bytes,
+                                               int sfb_stage_bytes) {
+  return 1024 /*alignment slack*/ + stages * (gemm_stage_bytes(BN) + sfa_stage_bytes + sfb_stage_bytes) +
+         256 /*barriers, TMEM slot, abort flag*/;
+}
+
+}  // namespace b200
