@@ -1,0 +1,490 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-GEMM path on B200 (and of the reference's CPU path).
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload NAME]
+
+One "step" is one GEMM call of the workload.  The default workload is the
+headline single-GPU configuration: MX fp8 `GemmMxE4M3`, M=N=K=4096, TN,
+alpha=1, beta=0.5, E8M0 scales in [122,132], C ~ N(0,1).  With N > 1 ranks
+(torchrun, one process per GPU) the output is sharded by row blocks: every rank
+owns a 4096-row block of a (4096*N) x 4096 x 4096 problem and all of B (weak
+scaling, no data-path collective).
+
+Prints ONE JSON line (rank 0).  `value` is device-resident throughput (CUDA
+events around K asynchronous calls, max over ranks); `e2e` is the same metric
+through the synchronous C-ABI call with pinned HOST buffers, host<->device
+copies included; `roofline` is the tensor-core kernel alone, timed live with
+CUDA events on its stream; `cpu_baseline` is the reference's own CPU operator
+(oracle/_ref, built from the unmodified reference headers) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return d, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# ---------------------------------------------------------------------------------
+# workloads
+# ---------------------------------------------------------------------------------
+class Workload:
+    """A GEMM configuration: host operand generation, argument construction,
+    algorithmic work."""
+
+    def __init__(self, name):
+        from cpu_ops_b200 import _capi
+        self.name = name
+        self.kind = "mx"
+        self.fmt = _capi.FMT_E4M3
+        self.m = self.n = self.k = 4096
+        self.alpha, self.beta = 1.0, 0.5
+        self.scale_lo, self.scale_hi = 122, 132
+        self.split_k = 0
+        self.chain = None
+        self.bound = "tensor"
+        if name == "mxfp8_e4m3_4096":
+            pass
+        elif name == "int8_2048":
+            self.kind, self.m, self.n, self.k = "int8", 2048, 2048, 2048
+            self.alpha, self.beta, self.split_k = 1, 1, 1
+        elif name == "int8_8192_chain":
+            self.kind, self.m, self.n, self.k = "int8", 8192, 8192, 16384
+            self.alpha, self.beta, self.chain = 1, 0, "bias_relu_clamp"
+        elif name == "int8_8192":
+            self.kind, self.m, self.n, self.k = "int8", 8192, 8192, 8192
+            self.alpha, self.beta = 1, 0
+        elif name in ("mxfp8_8192", "mxfp4_8192"):
+            self.fmt = _capi.FMT_E4M3 if name == "mxfp8_8192" else _capi.FMT_E2M1
+            self.m = self.n = self.k = 8192
+            self.beta = 0.0
+        elif name in ("mx_e5m2_16384", "mx_e2m1_16384"):
+            self.fmt = _capi.FMT_E5M2 if "e5m2" in name else _capi.FMT_E2M1
+            self.m = self.n = self.k = 16384
+            self.beta, self.scale_lo, self.scale_hi = 0.0, 120, 134
+        elif name.startswith("mxfp4_decode_m"):
+            self.fmt = _capi.FMT_E2M1
+            self.m, self.n, self.k = int(name.rsplit("m", 1)[1]), 14336, 4096
+            self.beta, self.scale_lo, self.scale_hi = 0.0, 124, 130
+            self.bound = "hbm"
+        else:
+            raise SystemExit(f"unknown workload {name}")
+
+    # algorithmic work of one step for `rows` output rows
+    def ops(self, rows=None):
+        rows = self.m if rows is None else rows
+        return 2.0 * rows * self.n * self.k
+
+    def min_bytes(self, rows=None):
+        from cpu_ops_b200 import workloads as W
+        rows = self.m if rows is None else rows
+        if self.kind == "int8":
+            return W.gemm_min_bytes(rows, self.n, self.k, 1, 1, False, self.beta != 0,
+                                    self.chain is not None)
+        b = W.FMT_BYTES_PER_ELEM[self.fmt]
+        return W.gemm_min_bytes(rows, self.n, self.k, b, b, True, self.beta != 0)
+
+    def host_operands(self, seed, rows=None):
+        """dict of flat numpy arrays for `rows` output rows (default: all)."""
+        from cpu_ops_b200 import workloads as W
+        rows = self.m if rows is None else rows
+        if self.kind == "int8":
+            P = W.int8_problem(rows, self.n, self.k, True, True, True, seed=seed)
+            out = dict(A=P.A, B=P.B, C=P.C, D=np.zeros_like(P.C))
+            if self.chain:
+                out["bias"] = W.rng_for(seed, 9).integers(-(1 << 15), (1 << 15) + 1, size=self.n,
+                                                          dtype=np.int32)
+            return out
+        P = W.mx_problem(self.fmt, rows, self.n, self.k, True, scale_lo=self.scale_lo,
+                         scale_hi=self.scale_hi, seed=seed)
+        return dict(A=P.A, SA=P.SA, B=P.B, SB=P.SB, C=P.C, D=np.zeros_like(P.C))
+
+    def operator(self, **kw):
+        import cpu_ops_b200 as c
+        if self.kind == "int8":
+            return c.GemmU8S8S32(c.RowMajor, c.RowMajor, c.RowMajor, **kw)
+        st = {2: c.fp8e4m3_t, 3: c.fp8e5m2_t, 4: c.fp4e2m1_t}[self.fmt]
+        return c.GemmMx(st, st, c.RowMajor, **kw)
+
+    def arguments(self, op, bufs, rows=None):
+        """bufs: dict name -> anything with a pointer (numpy array / torch tensor)."""
+        import cpu_ops_b200 as c
+        rows = self.m if rows is None else rows
+        n, k = self.n, self.k
+        if self.kind == "int8":
+            chain = []
+            if self.chain:
+                chain = [c.BiasAdd(bufs["bias"]), c.Relu(), c.Clamp(0, 1 << 20)]
+            epi = c.LinearCombinationFused(self.alpha, self.beta, chain)
+            return op.Arguments(c.GemmCoord(rows, n, k), c.TensorRef(bufs["A"], k),
+                                c.TensorRef(bufs["B"], n), c.TensorRef(bufs["C"], n),
+                                c.TensorRef(bufs["D"], n), epi, self.split_k)
+        kg = (k + 31) // 32
+        return op.Arguments(c.GemmCoord(rows, n, k), c.MxTensorRef(bufs["A"], bufs["SA"], k, kg),
+                            c.MxTensorRef(bufs["B"], bufs["SB"], k, kg), c.TensorRef(bufs["C"], n),
+                            c.TensorRef(bufs["D"], n), c.LinearCombination(self.alpha, self.beta),
+                            self.split_k)
+
+    def reference_call(self, ref, h, rows, threads=0):
+        """One call of the reference's CPU operator on host arrays `h`."""
+        n, k = self.n, self.k
+        if self.kind == "int8":
+            if self.chain:
+                return ref.gemm_u8s8s32_bias_relu_clamp(rows, n, k, h["A"], k, h["B"], n, h["C"], n,
+                                                        h["D"], n, self.alpha, self.beta, h["bias"],
+                                                        0, 1 << 20, self.split_k, threads)
+            return ref.gemm_u8s8s32(rows, n, k, h["A"], k, True, h["B"], n, True, h["C"], n, h["D"],
+                                    n, True, self.alpha, self.beta, False, self.split_k, threads)
+        kg = (k + 31) // 32
+        return ref.gemm_mx(rows, n, k, self.fmt, h["A"], h["SA"], k, kg, self.fmt, h["B"], h["SB"],
+                           k, kg, h["C"], n, h["D"], n, True, self.alpha, self.beta, False,
+                           self.split_k, threads)
+
+    @property
+    def dtype(self):
+        from cpu_ops_b200 import _capi
+        return {"int8": "u8*s8->s32"}.get(self.kind) or {
+            _capi.FMT_E4M3: "mxfp8 e4m3 (f32 accumulate)", _capi.FMT_E5M2: "mxfp8 e5m2 (f32 accumulate)",
+            _capi.FMT_E2M1: "mxfp4 e2m1 (f32 accumulate)"}[self.fmt]
+
+    @property
+    def peak_factor(self):
+        """Dense tensor peak relative to bf16: int8/fp8 x2, fp4 x4."""
+        from cpu_ops_b200 import _capi
+        return 4.0 if (self.kind == "mx" and self.fmt == _capi.FMT_E2M1) else 2.0
+
+
+# ---------------------------------------------------------------------------------
+# CPU baseline: the reference's own operator on the host cores
+# ---------------------------------------------------------------------------------
+def time_reference(wl: Workload, steps: int, warmup: int, budget_s: float = 20.0):
+    """Times oracle/_ref (the unmodified reference headers) the way the
+    reference's benchmark does: warm-up, then wall clock around op(args) with
+    all hardware threads (examples/01_benchmark.cc:25-35,96-101).  Each step is
+    a bounded row-block sample of the workload."""
+    from oracle.loader import Reference, have_reference
+    if not have_reference():
+        return None
+    ref = Reference()
+    # calibrate the sample so that the whole run stays near the budget
+    rows = min(wl.m, 256)
+    h = wl.host_operands(seed=1234, rows=rows)
+    t0 = time.perf_counter()
+    wl.reference_call(ref, h, rows)
+    t_probe = max(time.perf_counter() - t0, 1e-4)
+    per_row = t_probe / rows
+    total_calls = max(1, steps + warmup)
+    rows_budget = int(budget_s / total_calls / per_row)
+    rows = max(min(wl.m, rows_budget), min(wl.m, 128))
+    if rows >= 128:
+        rows = rows // 128 * 128
+    h = wl.host_operands(seed=1234, rows=rows)
+    for _ in range(warmup):
+        wl.reference_call(ref, h, rows)
+    times = []
+    t_all0 = time.perf_counter()
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        wl.reference_call(ref, h, rows)
+        times.append(time.perf_counter() - t0)
+    t_all = time.perf_counter() - t_all0
+    return dict(rows=rows, mean_s=t_all / steps, best_s=min(times), isa=ref.isa,
+                threads=ref.pool_threads, lib=ref.path.name)
+
+
+def rate_of(wl: Workload, rows, seconds):
+    if wl.bound == "hbm":
+        return wl.min_bytes(rows) / seconds / 1e9, "GB/s"
+    return wl.ops(rows) / seconds / 1e12, "TFLOP/s" if wl.kind == "mx" else "TOP/s"
+
+
+# ---------------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------------
+class ClockSampler(threading.Thread):
+    """Samples SM clock and clock-event reasons of one GPU through NVML."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+               0x4: "sw_power_cap", 0x80: "hw_power_brake", 0x2: "applications_clocks_setting"}
+
+    def __init__(self, index, period_s=0.004):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period_s
+        self.samples, self.mark = [], None
+        self._stop = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.max_mhz = None
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                try:
+                    reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                self.samples.append((time.perf_counter(), mhz, reasons))
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def stop(self):
+        self._stop.set()
+
+    def summary(self, t0, t1):
+        inside = [s for s in self.samples if t0 <= s[0] <= t1] or self.samples
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        mhz = sorted(s[1] for s in inside)
+        bits = 0
+        for s in inside:
+            bits |= s[2]
+        reasons = [name for bit, name in self.REASONS.items() if bits & bit]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": self.max_mhz, "reasons": reasons,
+                "samples": len(inside)}
+
+
+# ---------------------------------------------------------------------------------
+def run_reference_arm(args, wl, rank, world):
+    if rank != 0:
+        return 0
+    r = time_reference(wl, args.steps, args.warmup)
+    if r is None:
+        print(json.dumps({"impl": "reference",
+                          "unavailable": "oracle/_ref is not built (reference checkout absent at build time)"}))
+        return 0
+    value, unit = rate_of(wl, r["rows"], r["mean_s"])
+    sample = (f"{r['rows']} of {wl.m} output rows x N={wl.n} x K={wl.k} per step, "
+              f"{r['lib']} ({r['isa']}), {r['threads']} threads")
+    line = {
+        "impl": "reference", "metric": metric_name(wl), "value": value, "unit": unit,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": r["mean_s"] * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+        "config": config_of(wl, world),
+        "cpu_baseline": {"value": value, "unit": unit, "cores": r["threads"], "kind": "reference",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def metric_name(wl):
+    if wl.bound == "hbm":
+        return f"decode GEMM HBM GB/s ({wl.name})"
+    return f"{'int8' if wl.kind == 'int8' else ('mxfp4' if wl.peak_factor == 4 else 'mxfp8')} GEMM " \
+           f"{'TOPS' if wl.kind == 'int8' else 'TFLOPS'} ({wl.name}, whole job)"
+
+
+def config_of(wl, world):
+    return {"workload": wl.name, "m_per_gpu": wl.m, "n": wl.n, "k": wl.k, "alpha": wl.alpha,
+            "beta": wl.beta, "layout": "TN" if wl.kind == "mx" else "all RowMajor",
+            "sharding": f"output row blocks over {world} rank(s), B replicated, no collective",
+            "l2": "operands rotate over 3 distinct buffer sets whose total size exceeds the L2"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="mxfp8_e4m3_4096")
+    ap.add_argument("--tile-n", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    wl = Workload(args.workload)
+
+    if args.impl == "reference":
+        return run_reference_arm(args, wl, rank, world)
+
+    import torch
+    import torch.distributed as dist
+    import cpu_ops_b200 as c
+    from cpu_ops_b200 import _capi
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback in the product)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _capi.load()
+    peaks, peak_kind = load_peaks()
+
+    # ---- operands: 3 rotating device sets (distinct data), this rank's row block ----
+    n_sets = 3
+    sets, host0 = [], None
+    for s in range(n_sets):
+        h = wl.host_operands(seed=1000 * rank + s)
+        if s == 0:
+            host0 = h
+        sets.append({k_: torch.from_numpy(v).to(dev) for k_, v in h.items()})
+    stream = torch.cuda.current_stream().cuda_stream
+    op = wl.operator(stream=stream, asynchronous=True, tile_n=args.tile_n)
+    arg_sets = [wl.arguments(op, b) for b in sets]
+
+    def step(i):
+        st = op(arg_sets[i % n_sets])
+        if st != c.Status.kSuccess:
+            raise RuntimeError(f"GEMM failed: {st!r}: {_capi.last_error()}")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    if c.stream_status(stream) != c.Status.kSuccess:
+        raise RuntimeError("device-side error during warm-up: " + _capi.last_error())
+    launches0 = c.launch_count()
+    lib.cpuops_b200_profile(1)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_wall0 = time.perf_counter()
+    ev0.record()
+    for i in range(args.steps):
+        step(i)
+    ev1.record()
+    barrier()
+    t_wall1 = time.perf_counter()
+    lib.cpuops_b200_profile(0)
+    launches = c.launch_count() - launches0
+    ms = ev0.elapsed_time(ev1)
+    import ctypes as C
+    kms, kn = C.c_double(0), C.c_int32(0)
+    lib.cpuops_b200_profile_collect(C.byref(kms), C.byref(kn))
+    if c.stream_status(stream) != c.Status.kSuccess:
+        raise RuntimeError("device-side error during the timed region: " + _capi.last_error())
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    clocks = sampler.summary(t_wall0, t_wall1)
+
+    # ---- end to end: pinned host buffers through the synchronous call ----
+    e2e = None
+    if not args.no_e2e:
+        pinned = {k_: torch.from_numpy(v).pin_memory() for k_, v in host0.items()}
+        op_sync = wl.operator(tile_n=args.tile_n)
+        a_sync = wl.arguments(op_sync, pinned)
+        e2e_steps = max(3, min(args.steps, 30))
+        for _ in range(2):
+            op_sync(a_sync)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            st = op_sync(a_sync)
+            if st != c.Status.kSuccess:
+                raise RuntimeError(f"e2e GEMM failed: {st!r}: {_capi.last_error()}")
+        t_e2e = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([t_e2e], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            t_e2e = float(t.item())
+        h2d = sum(v.numel() * v.element_size() for k_, v in pinned.items()
+                  if k_ != "D" and not (k_ == "C" and wl.beta == 0))
+        d2h = pinned["D"].numel() * pinned["D"].element_size()
+        ev, eu = rate_of(wl, wl.m * world, t_e2e / e2e_steps)
+        e2e = {"value": ev, "unit": eu, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+               "ms_per_step": t_e2e / e2e_steps * 1e3, "steps": e2e_steps}
+    sampler.stop()
+
+    if rank == 0:
+        sec_per_step = ms / 1e3 / args.steps
+        value, unit = rate_of(wl, wl.m * world, sec_per_step)
+        # roofline of the dominant (tensor-core) kernel, per launch
+        k_avg_s = (kms.value / 1e3 / kn.value) if kn.value else None
+        if wl.bound == "hbm":
+            peak = float(peaks["hbm_gbs"])
+            achieved = wl.min_bytes() / k_avg_s / 1e9 if k_avg_s else None
+            r_unit, basis = "GB/s", f"hbm_gbs ({peak_kind})"
+        else:
+            peak = wl.peak_factor * float(peaks["bf16_tflops"])
+            achieved = wl.ops() / k_avg_s / 1e12 if k_avg_s else None
+            r_unit = "TFLOP/s"
+            basis = (f"{wl.peak_factor:g} x bf16_tflops burst ({peak_kind}): dense "
+                     f"{'fp4' if wl.peak_factor == 4 else 'int8/fp8'} is nominally "
+                     f"{wl.peak_factor:g}x bf16; no 8/4-bit peak was measured on this pool")
+        traffic = KERNEL_DRAM_TRAFFIC.get(wl.name)
+        roofline = {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": r_unit,
+                    "frac": (achieved / peak) if achieved else None, "traffic": traffic,
+                    "kernel": "gemm_tcgen05_kernel", "kernel_ms": (k_avg_s * 1e3) if k_avg_s else None,
+                    "timed_launches": kn.value, "peak_basis": basis,
+                    "algorithmic_per_launch": wl.ops() if wl.bound == "tensor" else wl.min_bytes()}
+        line = {
+            "metric": metric_name(wl), "value": value, "unit": unit, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
+            "data": "synthetic", "config": config_of(wl, world), "clocks": clocks,
+            "gpu_launches": int(launches), "roofline": roofline, "impl": "b200",
+        }
+        if e2e:
+            line["e2e"] = e2e
+        if world == 1 and not args.no_cpu_baseline:
+            r = time_reference(wl, steps=3, warmup=1, budget_s=15.0)
+            if r is not None:
+                cv, cu = rate_of(wl, r["rows"], r["best_s"])
+                line["cpu_baseline"] = {
+                    "value": cv, "unit": cu, "cores": r["threads"], "kind": "reference",
+                    "sample": f"{r['rows']} of {wl.m} output rows x N={wl.n} x K={wl.k}, best of 3, "
+                              f"{r['lib']} ({r['isa']})"}
+            else:
+                line["cpu_baseline"] = {"value": None, "unit": unit, "cores": 0, "kind": "reference",
+                                        "sample": "oracle/_ref not built"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of gemm_tcgen05_kernel from
+# the ncu captures summarised under profiles/ (None until captured for that workload).
+KERNEL_DRAM_TRAFFIC = {}
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -37,6 +37,8 @@ EXPORTED_SYMBOLS = (
     "cpuops_b200_scale_layout_bytes",
     "cpuops_b200_shard_rows",
     "cpuops_b200_stream_status",
+    "cpuops_b200_profile",
+    "cpuops_b200_profile_collect",
     "cpuops_b200_launch_count",
     "cpuops_b200_last_error",
     "cpuops_b200_abi_version",
@@ -93,6 +95,10 @@ def load() -> C.CDLL:
                                            C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
     lib.cpuops_b200_stream_status.restype = C.c_int
     lib.cpuops_b200_stream_status.argtypes = [C.c_void_p]
+    lib.cpuops_b200_profile.restype = C.c_int
+    lib.cpuops_b200_profile.argtypes = [C.c_int]
+    lib.cpuops_b200_profile_collect.restype = C.c_int
+    lib.cpuops_b200_profile_collect.argtypes = [C.POINTER(C.c_double), C.POINTER(C.c_int32)]
     lib.cpuops_b200_launch_count.restype = C.c_uint64
     lib.cpuops_b200_last_error.restype = C.c_char_p
     lib.cpuops_b200_abi_version.restype = C.c_int

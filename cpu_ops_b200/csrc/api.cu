@@ -71,6 +71,10 @@ struct DeviceState {
   std::map<cudaStream_t, Workspace> ws;
 };
 
+// Optional timing of the tensor-core kernel alone (events on the launching stream).
+bool g_profile = false;
+std::vector<std::pair<cudaEvent_t, cudaEvent_t>> g_profile_events;
+
 std::mutex g_mu;  // serialises calls (the CPU library serialises on its pool mutex too)
 DeviceState g_dev[64];
 EncodeTiledFn g_encode = nullptr;
@@ -352,6 +356,31 @@ CPUOPS_B200_API int cpuops_b200_stream_status(void* stream) {
     CUDA_TRY(cudaStreamSynchronize(s));
     return CPUOPS_B200_STATUS_DEVICE_TIMEOUT;
   }
+  return 0;
+}
+
+CPUOPS_B200_API int cpuops_b200_profile(int enable) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  g_profile = enable != 0;
+  return 0;
+}
+
+CPUOPS_B200_API int cpuops_b200_profile_collect(double* total_ms, int32_t* launches) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  double sum = 0.0;
+  int n = 0;
+  for (auto& pr : g_profile_events) {
+    CUDA_TRY(cudaEventSynchronize(pr.second));
+    float ms = 0.f;
+    CUDA_TRY(cudaEventElapsedTime(&ms, pr.first, pr.second));
+    sum += ms;
+    ++n;
+    cudaEventDestroy(pr.first);
+    cudaEventDestroy(pr.second);
+  }
+  g_profile_events.clear();
+  if (total_ms) *total_ms = sum;
+  if (launches) *launches = n;
   return 0;
 }
 
@@ -795,6 +824,12 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
                               120 * 1024);
     const int64_t total_tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles * p.slices;
     const unsigned grid = static_cast<unsigned>(std::min<int64_t>(total_tiles, st.sm_count));
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    if (g_profile) {
+      CUDA_TRY(cudaEventCreate(&ev0));
+      CUDA_TRY(cudaEventCreate(&ev1));
+      CUDA_TRY(cudaEventRecord(ev0, stream));
+    }
     if (kind == kKindI8) {
       gemm_tcgen05_kernel<kKindI8><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, p);
     } else if (kind == kKindMxf8) {
@@ -804,6 +839,10 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
     }
     g_launches.fetch_add(1);
     CUDA_TRY(cudaGetLastError());
+    if (g_profile) {
+      CUDA_TRY(cudaEventRecord(ev1, stream));
+      g_profile_events.emplace_back(ev0, ev1);
+    }
     if (ch.slices > 1) {
       const int64_t total = static_cast<int64_t>(Mk) * Nk;
       if (is_mx) {

@@ -176,6 +176,13 @@ CPUOPS_B200_API int cpuops_b200_shard_rows(int32_t m, int32_t world, int32_t ran
 /* Status of work enqueued with FLAG_ASYNC on `stream` (synchronises it). */
 CPUOPS_B200_API int cpuops_b200_stream_status(void* stream);
 
+/* Measurement aid with no counterpart in the reference: while enabled, CUDA
+ * events are recorded on the launching stream around every tensor-core GEMM
+ * kernel (not the helper kernels).  collect() waits for them, returns the
+ * summed device time and the number of timed launches, and forgets them. */
+CPUOPS_B200_API int cpuops_b200_profile(int enable);
+CPUOPS_B200_API int cpuops_b200_profile_collect(double* total_ms, int32_t* launches);
+
 /* Kernels launched by this library in this process so far (all threads). */
 CPUOPS_B200_API uint64_t cpuops_b200_launch_count(void);
 
