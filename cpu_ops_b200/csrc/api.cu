@@ -15,6 +15,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -302,8 +303,7 @@ CPUOPS_B200_API size_t cpuops_b200_scale_layout_bytes(int32_t rows, int32_t k, i
   return static_cast<size_t>(tiles * stages * (blocks_per_stage / 4) * nb128 * 512);
 }
 
-static int launch_relayout(const void* scales, int rows, int k, int ld, int tile_rows, int bps,
-                           void* out, cudaStream_t stream) {
+static ScaleLayout make_scale_layout(int rows, int k, int ld, int tile_rows, int bps) {
   ScaleLayout L;
   L.rows = rows;
   L.kblocks = (k + 31) / 32;
@@ -314,11 +314,19 @@ static int launch_relayout(const void* scales, int rows, int k, int ld, int tile
   L.ka = bps / 4;
   L.tiles = (rows + tile_rows - 1) / tile_rows;
   L.stages = (k + bps * 32 - 1) / (bps * 32);
-  const int64_t atoms = static_cast<int64_t>(L.tiles) * L.stages * L.ka * L.nb128;
+  return L;
+}
+
+// Re-lays-out one scale array, or two (src1 != nullptr) in a single launch.
+static int launch_relayout(const void* src0, void* dst0, const ScaleLayout& L0, const void* src1,
+                           void* dst1, const ScaleLayout& L1, cudaStream_t stream) {
+  int64_t atoms = static_cast<int64_t>(L0.tiles) * L0.stages * L0.ka * L0.nb128;
+  if (src1) atoms += static_cast<int64_t>(L1.tiles) * L1.stages * L1.ka * L1.nb128;
   const int threads = 256;
   const int64_t blocks = std::min<int64_t>((atoms * 32 + threads - 1) / threads, 148 * 16);
   relayout_scales_kernel<<<static_cast<unsigned>(std::max<int64_t>(blocks, 1)), threads, 0, stream>>>(
-      static_cast<const uint8_t*>(scales), static_cast<uint8_t*>(out), L);
+      static_cast<const uint8_t*>(src0), static_cast<uint8_t*>(dst0), L0,
+      static_cast<const uint8_t*>(src1), static_cast<uint8_t*>(dst1), L1);
   g_launches.fetch_add(1);
   CUDA_TRY(cudaGetLastError());
   return 0;
@@ -336,8 +344,8 @@ CPUOPS_B200_API int cpuops_b200_relayout_scales(const void* scales, int32_t rows
   DeviceState* st = nullptr;
   if (int rc = init_device(-1, &st)) return rc;
   cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : st->stream;
-  if (int rc = launch_relayout(scales, rows, k, ld_scales, tile_rows, blocks_per_stage, out, s))
-    return rc;
+  const ScaleLayout L = make_scale_layout(rows, k, ld_scales, tile_rows, blocks_per_stage);
+  if (int rc = launch_relayout(scales, out, L, nullptr, nullptr, L, s)) return rc;
   if (!stream) CUDA_TRY(cudaStreamSynchronize(s));
   return 0;
 }
@@ -750,8 +758,9 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
       const uint8_t* sbk = swap ? sa_ptr : sb_ptr;
       const int ldsak = swap ? d->ld_scales_b : d->ld_scales_a;
       const int ldsbk = swap ? d->ld_scales_a : d->ld_scales_b;
-      if (int rc = launch_relayout(sak, Mk, k, ldsak, kTileM, bps, wsp + off_sfa, stream)) return rc;
-      if (int rc = launch_relayout(sbk, Nk, k, ldsbk, ch.BN, bps, wsp + off_sfb, stream)) return rc;
+      if (int rc = launch_relayout(sak, wsp + off_sfa, make_scale_layout(Mk, k, ldsak, kTileM, bps), sbk,
+                                   wsp + off_sfb, make_scale_layout(Nk, k, ldsbk, ch.BN, bps), stream))
+        return rc;
     }
 
     // ---- tensor maps -----------------------------------------------------------------------
@@ -811,7 +820,9 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
       }
     }
     p.error = st.error_dev;
-    const int per_stage = gemm_stage_bytes(ch.BN) + p.sfa_stage_bytes + p.sfb_stage_bytes;
+    if (const char* dbg = getenv("CPUOPS_B200_DEBUG")) p.debug_flags = atoi(dbg);
+    const int sf_stage_bytes = p.sfa_stage_bytes + p.sfb_stage_bytes;
+    const int per_stage = gemm_stage_bytes(ch.BN) + sf_stage_bytes;
     int stages = (st.smem_optin - 1024 - 256) / per_stage;
     stages = std::min({stages, kMaxStages, std::max(2, k_blocks)});
     if (stages < 2) {
@@ -820,7 +831,7 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
     }
     p.stages = stages;
     // At least 120 KB so that two CTAs never share an SM: each allocates all of tensor memory.
-    const int smem = std::max(gemm_smem_bytes(ch.BN, stages, p.sfa_stage_bytes, p.sfb_stage_bytes),
+    const int smem = std::max(gemm_smem_bytes(ch.BN, stages, sf_stage_bytes),
                               120 * 1024);
     const int64_t total_tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles * p.slices;
     const unsigned grid = static_cast<unsigned>(std::min<int64_t>(total_tiles, st.sm_count));

@@ -144,6 +144,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int stages = p.stages;
   const int stage_bytes = gemm_stage_bytes(p.BN);
+  // Each stage also carries the k-block's scale factors (MX), in a separate region so
+  // that the operand tiles stay 1024-byte aligned.
   const int sf_stage = p.sfa_stage_bytes + p.sfb_stage_bytes;
   const uint32_t sf_base = smem_base + stages * stage_bytes;
   const uint32_t bar_base = sf_base + stages * sf_stage;
@@ -192,45 +194,59 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       uint32_t ph = 0, armed = 0, armed_parity = 0;
       bool ok = true;
       const uint32_t tx_bytes = static_cast<uint32_t>(stage_bytes + sf_stage);
+      const uint32_t full0 = full_bar(0), empty0 = empty_bar(0);
+      uint32_t full_addr = full0, empty_addr = empty0, a_dst = smem_base, sf_dst = sf_base;
+      const int a_mn = p.a_mn_major, b_mn = p.b_mn_major, b_chunks = p.BN / 128;
+      const uint32_t sfa_bytes = p.sfa_stage_bytes, sfb_bytes = p.sfb_stage_bytes;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const TileCoord tc = decode_tile(p, t);
         const int m0 = tc.m_tile * kTileM, n0 = tc.n_tile * p.BN;
-        for (int i = 0; i < tc.nkb; ++i) {
-          const int kb = tc.kb0 + i;
-          if (!mbar_wait_bounded(empty_bar(s), ph ^ 1u, abort_flag)) {
+        int kx = tc.kb0 * 128;  // k coordinate (bytes along k) of the next block
+        const uint8_t* sfa_src = nullptr;
+        const uint8_t* sfb_src = nullptr;
+        if constexpr (kMx) {
+          sfa_src = p.sfa + (static_cast<int64_t>(tc.m_tile) * p.k_blocks + tc.kb0) * p.sfa_stage_bytes;
+          sfb_src = p.sfb + (static_cast<int64_t>(tc.n_tile) * p.k_blocks + tc.kb0) * p.sfb_stage_bytes;
+        }
+        for (int i = 0; i < tc.nkb; ++i, kx += 128) {
+          if (!mbar_wait_bounded(empty_addr, ph ^ 1u, abort_flag)) {
             record_error(p, abort_flag, kErrProducerWait);
             ok = false;
             break;
           }
-          const uint32_t bar = full_bar(s);
-          mbar_expect_tx(bar, tx_bytes);
+          mbar_expect_tx(full_addr, tx_bytes);
           armed |= 1u << s;
           armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
-          const uint32_t a_dst = smem_base + s * stage_bytes;
           const uint32_t b_dst = a_dst + kTileM * 128;
-          if (!p.a_mn_major) {
-            tma_load_2d(a_dst, &tmA, bar, kb * 128, m0);
+          if (!a_mn) {
+            tma_load_2d(a_dst, &tmA, full_addr, kx, m0);
           } else {
-            tma_load_2d(a_dst, &tmA, bar, m0, kb * 128);
+            tma_load_2d(a_dst, &tmA, full_addr, m0, kx);
           }
-          if (!p.b_mn_major) {
-            tma_load_2d(b_dst, &tmB, bar, kb * 128, n0);
+          if (!b_mn) {
+            tma_load_2d(b_dst, &tmB, full_addr, kx, n0);
           } else {
-            for (int c = 0; c < p.BN / 128; ++c)
-              tma_load_2d(b_dst + c * 16384, &tmB, bar, n0 + c * 128, kb * 128);
+            for (int c = 0; c < b_chunks; ++c)
+              tma_load_2d(b_dst + c * 16384, &tmB, full_addr, n0 + c * 128, kx);
           }
           if constexpr (kMx) {
-            const uint32_t sfa_dst = sf_base + s * sf_stage;
-            bulk_load(sfa_dst,
-                      p.sfa + (static_cast<int64_t>(tc.m_tile) * p.k_blocks + kb) * p.sfa_stage_bytes,
-                      p.sfa_stage_bytes, bar);
-            bulk_load(sfa_dst + p.sfa_stage_bytes,
-                      p.sfb + (static_cast<int64_t>(tc.n_tile) * p.k_blocks + kb) * p.sfb_stage_bytes,
-                      p.sfb_stage_bytes, bar);
+            bulk_load(sf_dst, sfa_src, sfa_bytes, full_addr);
+            bulk_load(sf_dst + sfa_bytes, sfb_src, sfb_bytes, full_addr);
+            sfa_src += sfa_bytes;
+            sfb_src += sfb_bytes;
           }
           if (++s == stages) {
             s = 0;
             ph ^= 1u;
+            full_addr = full0;
+            empty_addr = empty0;
+            a_dst = smem_base;
+            sf_dst = sf_base;
+          } else {
+            full_addr += 8;
+            empty_addr += 8;
+            a_dst += stage_bytes;
+            sf_dst += sf_stage;
           }
         }
       }
@@ -244,75 +260,112 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
+    // One thread feeds the tensor pipe.  A 128 x 256 x 32-byte MMA executes in 128
+    // cycles, so this thread has about that much time per instruction: the loop
+    // keeps every descriptor as a running 32-bit word and does no divisions,
+    // 64-bit arithmetic or parameter re-loads.
     if (lane == 0) {
-      int s = 0, it = 0;
-      uint32_t ph = 0;
       bool ok = true;
-      // K-major: rows of 128 bytes, 8-row groups 1024 bytes apart.  MN-major: the
-      // 128-byte rows run along m/n, k advances by rows; a second 128-column
-      // chunk of B starts 128 rows (16384 bytes) later.
-      const uint64_t a_hi = p.a_mn_major ? make_smem_desc_hi(16384, 1024, 2) : make_smem_desc_hi(16, 1024, 2);
-      const uint64_t b_hi = p.b_mn_major ? make_smem_desc_hi(16384, 1024, 2) : make_smem_desc_hi(16, 1024, 2);
-      const uint32_t a_step = p.a_mn_major ? 4096u : 32u;  // bytes per 32-byte k step
-      const uint32_t b_step = p.b_mn_major ? 4096u : 32u;
-      const uint64_t sf_hi = make_smem_desc_hi(0, 128, 0);  // 32 rows x 16 B, 8-row groups 128 B apart
+      // Matrix descriptors.  K-major: rows of 128 bytes, 8-row groups 1024 bytes
+      // apart.  MN-major: the 128-byte rows run along m/n and k advances by rows; a
+      // second 128-column chunk of B starts 128 rows (16384 bytes) later.
+      const uint64_t a_hi64 = p.a_mn_major ? make_smem_desc_hi(16384, 1024, 2) : make_smem_desc_hi(16, 1024, 2);
+      const uint64_t b_hi64 = p.b_mn_major ? make_smem_desc_hi(16384, 1024, 2) : make_smem_desc_hi(16, 1024, 2);
+      const uint64_t sf_hi64 = make_smem_desc_hi(0, 128, 0);  // 32 rows x 16 B, 8-row groups 128 B apart
+      const uint32_t a_hi = static_cast<uint32_t>(a_hi64 >> 32), b_hi = static_cast<uint32_t>(b_hi64 >> 32);
+      const uint32_t sf_hi = static_cast<uint32_t>(sf_hi64 >> 32);
+      const uint32_t a_lo0 = static_cast<uint32_t>(a_hi64) | (smem_base >> 4);
+      const uint32_t b_lo0 = static_cast<uint32_t>(b_hi64) | ((smem_base + kTileM * 128) >> 4);
+      const uint32_t stage_step = static_cast<uint32_t>(stage_bytes) >> 4;
+      const uint32_t a_k = p.a_mn_major ? 256u : 2u;  // descriptor step per 32-byte k step
+      const uint32_t b_k = p.b_mn_major ? 256u : 2u;
+      const uint32_t idesc = p.idesc;
+      uint32_t id1 = idesc, id2 = idesc, id3 = idesc;
+      if constexpr (KIND == kKindMxf8) {  // one scale byte per MMA: byte j of the column
+        id1 = idesc_with_sf_ids(idesc, 1, 1);
+        id2 = idesc_with_sf_ids(idesc, 2, 2);
+        id3 = idesc_with_sf_ids(idesc, 3, 3);
+      } else if constexpr (KIND == kKindMxf4) {  // two scale bytes per MMA: half-word j & 1
+        id1 = idesc_with_sf_ids(idesc, 2, 2);
+        id3 = id1;
+      }
       const uint32_t sf_col0 = static_cast<uint32_t>(nacc * p.BN);
-      const int sfa_atoms = p.sfa_stage_bytes / 512, sfb_atoms = p.sfb_stage_bytes / 512;
+      const uint32_t sfa_atoms = p.sfa_stage_bytes / 512, sfb_atoms = p.sfb_stage_bytes / 512;
+      const uint32_t sf_atoms = sfa_atoms + sfb_atoms;
+      // TMEM scale columns: the k-block's A atoms, then its B atoms (4 columns each)
       const uint32_t sfa_t = tmem_base + sf_col0;
       const uint32_t sfb_t = sfa_t + 4u * sfa_atoms;
-      const uint32_t sfb_k_stride = 4u * (sfb_atoms / 2);  // mxf4: columns per 4-block atom row
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+      const uint32_t sfa_half = 4u, sfb_half = 2u * sfb_atoms;  // mxf4: second 4-block atom row
+      const uint32_t sf_step = static_cast<uint32_t>(sf_stage) >> 4;
+      const uint32_t sf_lo0 = static_cast<uint32_t>(sf_hi64) | (sf_base >> 4);
+      const uint32_t full0 = full_bar(0), empty0 = empty_bar(0);
+
+      int s = 0, buf = 0;
+      uint32_t ph = 0, acc_ph = 0;
+      uint32_t a_lo = a_lo0, b_lo = b_lo0, full_addr = full0, empty_addr = empty0, sf_lo = sf_lo0;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const TileCoord tc = decode_tile(p, t);
-        const int buf = it % nacc;
-        const uint32_t acc_ph = static_cast<uint32_t>(it / nacc) & 1u;
         if (!mbar_wait_bounded(acc_empty_bar(buf), acc_ph ^ 1u, abort_flag)) {
           record_error(p, abort_flag, kErrMmaWaitAcc);
           break;
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * p.BN);
+        uint32_t accumulate = 0;
         for (int i = 0; i < tc.nkb; ++i) {
-          if (!mbar_wait_bounded(full_bar(s), ph, abort_flag)) {
+          if (!mbar_wait_bounded(full_addr, ph, abort_flag)) {
             record_error(p, abort_flag, kErrMmaWaitFull);
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t a_addr = smem_base + s * stage_bytes;
-          const uint32_t b_addr = a_addr + kTileM * 128;
           if constexpr (kMx) {
-            const uint32_t sf_s = sf_base + s * sf_stage;
-            for (int a = 0; a < sfa_atoms; ++a)
-              tmem_cp_32x128b_warpx4(sfa_t + 4u * a, smem_desc(sf_hi, sf_s + 512u * a));
-            for (int b = 0; b < sfb_atoms; ++b)
-              tmem_cp_32x128b_warpx4(sfb_t + 4u * b,
-                                     smem_desc(sf_hi, sf_s + p.sfa_stage_bytes + 512u * b));
+            // The k-block's scale factors: shared -> tensor memory.  Issued by the same
+            // thread ahead of the MMAs that read them, so the pipe orders them; the
+            // copies run while earlier MMAs are still executing.
+            uint32_t src = sf_lo, dst = sfa_t;
+            for (uint32_t a = 0; a < sf_atoms; ++a, src += 32, dst += 4)
+              tmem_cp_32x128b_warpx4_w(dst, src, sf_hi);
           }
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint64_t a_desc = smem_desc(a_hi, a_addr + j * a_step);
-            const uint64_t b_desc = smem_desc(b_hi, b_addr + j * b_step);
-            const uint32_t accumulate = (i > 0 || j > 0) ? 1u : 0u;
-            if constexpr (KIND == kKindI8) {
-              mma_i8(d_tmem, a_desc, b_desc, p.idesc, accumulate);
-            } else if constexpr (KIND == kKindMxf8) {
-              // one scale per row per MMA (k = 32): byte j of the scale column
-              mma_mxf8f6f4(d_tmem, a_desc, b_desc, idesc_with_sf_ids(p.idesc, j, j), sfa_t, sfb_t,
-                           accumulate);
-            } else {
-              // two scales per row per MMA (k = 64): half-word (j & 1) of atom j / 2
-              const uint32_t ka = static_cast<uint32_t>(j >> 1), id = static_cast<uint32_t>(j & 1) * 2u;
-              mma_mxf4(d_tmem, a_desc, b_desc, idesc_with_sf_ids(p.idesc, id, id), sfa_t + 4u * ka,
-                       sfb_t + sfb_k_stride * ka, accumulate);
-            }
+          if constexpr (KIND == kKindI8) {
+            mma_i8_w(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc, accumulate);
+            mma_i8_w(d_tmem, a_lo + a_k, a_hi, b_lo + b_k, b_hi, idesc, 1u);
+            mma_i8_w(d_tmem, a_lo + 2 * a_k, a_hi, b_lo + 2 * b_k, b_hi, idesc, 1u);
+            mma_i8_w(d_tmem, a_lo + 3 * a_k, a_hi, b_lo + 3 * b_k, b_hi, idesc, 1u);
+          } else if constexpr (KIND == kKindMxf8) {
+            mma_mxf8f6f4_w(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc, sfa_t, sfb_t, accumulate);
+            mma_mxf8f6f4_w(d_tmem, a_lo + 2, a_hi, b_lo + 2, b_hi, id1, sfa_t, sfb_t, 1u);
+            mma_mxf8f6f4_w(d_tmem, a_lo + 4, a_hi, b_lo + 4, b_hi, id2, sfa_t, sfb_t, 1u);
+            mma_mxf8f6f4_w(d_tmem, a_lo + 6, a_hi, b_lo + 6, b_hi, id3, sfa_t, sfb_t, 1u);
+          } else {
+            mma_mxf4_w(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc, sfa_t, sfb_t, accumulate);
+            mma_mxf4_w(d_tmem, a_lo + 2, a_hi, b_lo + 2, b_hi, id1, sfa_t, sfb_t, 1u);
+            mma_mxf4_w(d_tmem, a_lo + 4, a_hi, b_lo + 4, b_hi, id2, sfa_t + sfa_half, sfb_t + sfb_half, 1u);
+            mma_mxf4_w(d_tmem, a_lo + 6, a_hi, b_lo + 6, b_hi, id3, sfa_t + sfa_half, sfb_t + sfb_half, 1u);
           }
-          tc_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+          accumulate = 1u;
+          tc_commit(empty_addr);  // frees the stage once these MMAs (and copies) have read it
           if (++s == stages) {
             s = 0;
             ph ^= 1u;
+            a_lo = a_lo0;
+            b_lo = b_lo0;
+            full_addr = full0;
+            empty_addr = empty0;
+            sf_lo = sf_lo0;
+          } else {
+            a_lo += stage_step;
+            b_lo += stage_step;
+            full_addr += 8;
+            empty_addr += 8;
+            sf_lo += sf_step;
           }
         }
         if (ok) tc_commit(acc_full_bar(buf));
+        if (++buf == nacc) {
+          buf = 0;
+          acc_ph ^= 1u;
+        }
       }
       // Nothing may still be executing when tensor memory is released.
       tc_commit(drain_bar);
@@ -350,7 +403,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           if (lane == 0) mbar_arrive(acc_empty_bar(buf));
         }
         const int kcol0 = n0 + c * 32;
-        if (krow < p.Mk && kcol0 < p.Nk) store_chunk<kInt>(p, r, krow, kcol0, tc.slice);
+        if (krow < p.Mk && kcol0 < p.Nk && !(p.debug_flags & 4)) store_chunk<kInt>(p, r, krow, kcol0, tc.slice);
       }
     }
   }

@@ -72,15 +72,15 @@ struct GemmParams {
   // MX: re-laid-out scale factors, one contiguous chunk per (tile, stage)
   const uint8_t* sfa;
   const uint8_t* sfb;
-  int32_t sfa_stage_bytes, sfb_stage_bytes;
+  int32_t sfa_stage_bytes, sfb_stage_bytes;  // per k-block
   int32_t* error;           // device error word
+  int32_t debug_flags;      // experiments only (CPUOPS_B200_DEBUG)
 };
 
 // Shared-memory footprint of one launch of the GEMM kernel.
 __host__ __device__ inline int gemm_stage_bytes(int BN) { return kTileM * 128 + BN * 128; }
-__host__ __device__ inline int gemm_smem_bytes(int BN, int stages, int sfa_stage_bytes,
-                                               int sfb_stage_bytes) {
-  return 1024 /*alignment slack*/ + stages * (gemm_stage_bytes(BN) + sfa_stage_bytes + sfb_stage_bytes) +
+__host__ __device__ inline int gemm_smem_bytes(int BN, int stages, int sf_stage_bytes) {
+  return 1024 /*alignment slack*/ + stages * (gemm_stage_bytes(BN) + sf_stage_bytes) +
          256 /*barriers, TMEM slot, abort flag*/;
 }
 

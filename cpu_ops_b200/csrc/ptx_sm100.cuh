@@ -215,6 +215,73 @@ __device__ __forceinline__ void mma_mxf4(uint32_t d_tmem, uint64_t a_desc, uint6
       : "memory");
 }
 
+// Variants taking the two 32-bit halves of each matrix descriptor: only the low
+// word (start address) changes from one MMA to the next, so the issuing thread
+// keeps it in a 32-bit register and bumps it with one add.
+__device__ __forceinline__ void mma_i8_w(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                         uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %5, p;\n\t"
+      "}\n"
+      :
+      : "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_mxf8f6f4_w(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
+                                               uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                               uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], da, db, %5, [%7], [%8], p;\n\t"
+      "}\n"
+      :
+      : "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate),
+        "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+__device__ __forceinline__ void mma_mxf4_w(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                           uint32_t b_hi, uint32_t idesc, uint32_t sfa_tmem,
+                                           uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], da, db, %5, [%7], [%8], "
+      "p;\n\t"
+      "}\n"
+      :
+      : "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate),
+        "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4_w(uint32_t taddr, uint32_t src_lo,
+                                                         uint32_t src_hi) {
+  asm volatile(
+      "{\n\t"
+      ".reg .b64 ds;\n\t"
+      "mov.b64 ds, {%1, %2};\n\t"
+      "tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], ds;\n\t"
+      "}\n"
+      :
+      : "r"(taddr), "r"(src_lo), "r"(src_hi)
+      : "memory");
+}
+
 // Shared -> tensor memory copy of one scale-factor atom: 32 rows x 16 bytes of
 // shared memory land in 4 TMEM columns of lanes 0..31 and are replicated to the
 // other three lane quarters.

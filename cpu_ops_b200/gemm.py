@@ -217,7 +217,10 @@ class _Operator:
 
     def __init__(self, *, stream: Optional[int] = None, asynchronous: bool = False,
                  memory_space: int = _capi.MEM_AUTO, device: int = -1, tile_n: int = 0):
-        self._stream = stream
+        # A raw handle of 0 is CUDA's legacy default stream (what torch reports for its
+        # default stream); the C ABI reserves NULL for "the library's own stream", so
+        # pass the explicit legacy-stream handle instead.
+        self._stream = 1 if stream == 0 else stream
         self._async = asynchronous
         self._memory_space = memory_space
         self._device = device
@@ -311,7 +314,7 @@ def GemmMxE2M1(layout_c=RowMajor, **kw):
 
 def stream_status(stream: Optional[int] = None) -> Status:
     """Synchronise `stream` and report device-side errors of asynchronous calls."""
-    return Status(_capi.load().cpuops_b200_stream_status(stream))
+    return Status(_capi.load().cpuops_b200_stream_status(1 if stream == 0 else stream))
 
 
 def launch_count() -> int:

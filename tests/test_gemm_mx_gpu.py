@@ -96,11 +96,12 @@ def test_fused_float_chains(gpu, oracle):
     """BiasAdd/Relu/ScalePerRow/ScalePerCol/Clamp are exact f32 ops (same bits as
     applying them to the GEMM result); Gelu/Silu are compared with a tolerance."""
     m, n, k = 70, 150, 320
-    P = W.mx_problem(FMT_E4M3, m, n, k, True, pad=3, seed=24)
+    # scales 2^-8..2^-5 keep the results O(1), where test_fusion.cc's tolerance applies
+    P = W.mx_problem(FMT_E4M3, m, n, k, True, pad=3, seed=24, scale_lo=119, scale_hi=122)
     r = W.rng_for(24, 4)
-    v0 = (r.standard_normal(max(m, n)) * 4).astype(np.float32)
+    v0 = r.standard_normal(max(m, n)).astype(np.float32)
     v1 = (1.0 + 0.1 * r.standard_normal(max(m, n))).astype(np.float32)
-    alpha, beta = 0.01, 0.5
+    alpha, beta = 1.0, 0.5
     st, plain = run_mx_gpu(P, alpha, beta)
     assert st == c.Status.kSuccess
     chains = [
@@ -117,7 +118,8 @@ def test_fused_float_chains(gpu, oracle):
             assert st == c.Status.kSuccess, _capi.last_error()
             want = run_mx_oracle(oracle, P, alpha, beta, ops=ops)
             G = gather(D, m, n, P.ldc, True); R = gather(want, m, n, P.ldc, True)
-            assert np.allclose(G, R, rtol=1e-5, atol=1e-5)   # test/test_fusion.cc:89-93
+            tol = 1e-5 * np.maximum(1.0, np.abs(R))           # test/test_fusion.cc:89-93
+            assert np.all(np.abs(G - R) <= tol), float(np.max(np.abs(G - R) / tol))
             if exact and split == 1:
                 # chain(plain result) computed on the host from the GPU's own unfused output
                 ref_chain = _apply_chain_host(gather(plain, m, n, P.ldc, True), ops)
