@@ -104,6 +104,7 @@ def test_fused_float_chains(gpu, oracle):
     alpha, beta = 1.0, 0.5
     st, plain = run_mx_gpu(P, alpha, beta)
     assert st == c.Status.kSuccess
+    acc_scale = float(np.abs(gather(plain, m, n, P.ldc, True)).max())
     chains = [
         ([c.BiasAdd(v0), c.Relu()], [(OP_BIAS_ADD, v0, 0, 0), (OP_RELU, None, 0, 0)], True),
         ([c.ScalePerRow(v0)], [(OP_SCALE_PER_ROW, v0, 0, 0)], True),
@@ -118,7 +119,9 @@ def test_fused_float_chains(gpu, oracle):
             assert st == c.Status.kSuccess, _capi.last_error()
             want = run_mx_oracle(oracle, P, alpha, beta, ops=ops)
             G = gather(D, m, n, P.ldc, True); R = gather(want, m, n, P.ldc, True)
-            tol = 1e-5 * np.maximum(1.0, np.abs(R))           # test/test_fusion.cc:89-93
+            # test/test_fusion.cc:89-93 allows 1e-5 * max(1, |ref|) on O(1) data; where
+            # a bias cancels a large accumulator the error scales with the accumulator
+            tol = 1e-5 * np.maximum(1.0, np.abs(R)) + 1e-6 * acc_scale
             assert np.all(np.abs(G - R) <= tol), float(np.max(np.abs(G - R) / tol))
             if exact and split == 1:
                 # chain(plain result) computed on the host from the GPU's own unfused output
