@@ -48,7 +48,12 @@ def test_mx_golden(gpu):
     v0, v1 = z["ch_vec0"], z["ch_vec1"]
     chains = {1: [c.BiasAdd(v0), c.Relu()], 2: [c.ScalePerRow(v0)],
               3: [c.BiasAdd(v0), c.ScalePerCol(v1), c.Clamp(-0.5, 2.0)], 4: [c.Gelu()], 5: [c.Silu()]}
+    acc_scale = float(np.abs(z["ch_D1"]).max())
     for cid, chain in chains.items():
         st, D = run_mx_gpu(P, 0.01, 0.5, chain=chain)
         assert st == c.Status.kSuccess, _capi.last_error()
-        assert np.allclose(D, z[f"ch_D{cid}"], rtol=1e-5, atol=1e-5), cid
+        want = z[f"ch_D{cid}"]
+        # 1e-5 * max(1, |ref|) as in test/test_fusion.cc:89-93, plus a term for outputs
+        # where the bias cancels an accumulator of the data's overall magnitude
+        tol = 1e-5 * np.maximum(1.0, np.abs(want)) + 1e-6 * acc_scale
+        assert np.all(np.abs(D - want) <= tol), (cid, float(np.max(np.abs(D - want) / tol)))
