@@ -1,0 +1,3 @@
+// Drop-in path of the reference header of the same name; see cpu_ops/b200/core_types.h.
+#pragma once
+#include "cpu_ops/b200/core_types.h"
