@@ -29,10 +29,12 @@ ACT_NONE, ACT_RELU = 0, 1
 OP_RELU, OP_CLAMP, OP_BIAS_ADD, OP_SCALE_PER_ROW, OP_SCALE_PER_COL, OP_GELU, OP_SILU = range(1, 8)
 MEM_AUTO, MEM_HOST, MEM_DEVICE = 0, 1, 2
 FLAG_ASYNC = 1
+NOALLOC_SCRATCH_BYTES = 8 << 20
 
 # Every symbol include/cpu_ops_b200.h declares.
 EXPORTED_SYMBOLS = (
     "cpuops_b200_gemm",
+    "cpuops_b200_gemm_i8_noalloc",
     "cpuops_b200_relayout_scales",
     "cpuops_b200_scale_layout_bytes",
     "cpuops_b200_shard_rows",
@@ -85,6 +87,8 @@ def load() -> C.CDLL:
     lib = C.CDLL(str(LIB_PATH))
     lib.cpuops_b200_gemm.restype = C.c_int
     lib.cpuops_b200_gemm.argtypes = [C.POINTER(GemmDesc)]
+    lib.cpuops_b200_gemm_i8_noalloc.restype = C.c_int
+    lib.cpuops_b200_gemm_i8_noalloc.argtypes = [C.POINTER(GemmDesc)]
     lib.cpuops_b200_relayout_scales.restype = C.c_int
     lib.cpuops_b200_relayout_scales.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
                                                 C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]

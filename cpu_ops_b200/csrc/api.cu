@@ -886,4 +886,247 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
   return CPUOPS_B200_STATUS_SUCCESS;
 }
 
+
+}  // extern "C"
+
+// =================================================================================
+// Allocation-free split-k entry point
+// =================================================================================
+//
+// Some hosts of this library are not allowed to call cudaMalloc once they are up:
+// inference servers that hand all device memory to their own pool at start-up, and
+// latency-sensitive loops in which cudaMalloc/cudaFree would stall every stream of
+// the device.  The regular entry point grows a cached workspace with cudaMalloc the
+// first time a problem needs it.  cpuops_b200_gemm_i8_noalloc() below never does:
+// the split-k partial sums and the device error word live in the fixed array that
+// follows, which is part of the library image (each GPU that loads the library keeps
+// these bytes until the process exits).
+//
+// In host code the name `g_noalloc_scratch` is only a handle for the symbol, not a
+// device address, so the address is looked up once per device with
+// cudaGetSymbolAddress (with that device current) and that pointer is what the
+// kernels receive.
+#define CPUOPS_B200_NOALLOC_HEADER_BYTES 256u
+static __device__ __align__(256) unsigned char
+    g_noalloc_scratch[CPUOPS_B200_NOALLOC_HEADER_BYTES + CPUOPS_B200_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+
+struct NoAllocDevice {
+  bool ready = false;
+  unsigned char* scratch = nullptr;  // device address of g_noalloc_scratch on this device
+  int sm_count = 0;
+  int smem_optin = 0;
+};
+NoAllocDevice g_noalloc_dev[64];
+
+// One-time set-up for the current device: symbol address, device limits, kernel
+// attributes, the tensor-map encoder.  None of these allocate device memory.
+int noalloc_setup(int device, NoAllocDevice** out) {
+  NoAllocDevice& nd = g_noalloc_dev[device];
+  if (!nd.ready) {
+    int major = 0;
+    CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+    if (major != 10) {
+      set_error("device %d is not sm_100 (compute capability major %d)", device, major);
+      return CPUOPS_B200_STATUS_NO_DEVICE;
+    }
+    void* sym = nullptr;
+    CUDA_TRY(cudaGetSymbolAddress(&sym, g_noalloc_scratch));
+    if (!sym) {
+      set_error("cudaGetSymbolAddress returned a null address for the scratch array");
+      return CPUOPS_B200_STATUS_CUDA_ERROR;
+    }
+    nd.scratch = static_cast<unsigned char*>(sym);
+    CUDA_TRY(cudaDeviceGetAttribute(&nd.sm_count, cudaDevAttrMultiProcessorCount, device));
+    CUDA_TRY(cudaDeviceGetAttribute(&nd.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+    CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindI8>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, nd.smem_optin));
+    if (!g_encode) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult qres;
+      CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+      if (!fn || qres != cudaDriverEntryPointSuccess) {
+        set_error("cuTensorMapEncodeTiled is not exported by this driver");
+        return CPUOPS_B200_STATUS_CUDA_ERROR;
+      }
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    nd.ready = true;
+  }
+  *out = &nd;
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+CPUOPS_B200_API int cpuops_b200_gemm_i8_noalloc(const cpuops_b200_gemm_desc* d) {
+  if (!d || d->struct_size != sizeof(cpuops_b200_gemm_desc)) {
+    set_error("descriptor is null or struct_size does not match this library (ABI %d)",
+              CPUOPS_B200_ABI_VERSION);
+    return CPUOPS_B200_STATUS_BAD_DESCRIPTOR;
+  }
+  if (d->kind != CPUOPS_B200_KIND_I8 || d->a_format != CPUOPS_B200_FMT_U8 ||
+      d->b_format != CPUOPS_B200_FMT_S8) {
+    set_error("gemm_i8_noalloc handles the u8 x s8 -> s32 path only");
+    return CPUOPS_B200_STATUS_UNSUPPORTED;
+  }
+  if (d->n_ops < 0 || d->n_ops > CPUOPS_B200_MAX_OPS) return CPUOPS_B200_STATUS_BAD_DESCRIPTOR;
+  const int m = d->m, n = d->n, k = d->k;
+  if (m < 0 || n < 0 || k < 0) return CPUOPS_B200_STATUS_INVALID_PROBLEM;
+  if (m == 0 || n == 0) return CPUOPS_B200_STATUS_SUCCESS;
+  if (k == 0) {
+    set_error("gemm_i8_noalloc needs k > 0 (use cpuops_b200_gemm for the k == 0 epilogue)");
+    return CPUOPS_B200_STATUS_UNSUPPORTED;
+  }
+  const bool c_rm = d->c_row_major != 0;
+  if (!d->a || !d->b || !d->c || !d->d) return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+  if (d->lda < (d->a_row_major ? k : m) || d->ldb < (d->b_row_major ? n : k) ||
+      d->ldc < (c_rm ? n : m) || d->ldd < (c_rm ? n : m))
+    return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+  for (int t = 0; t < d->n_ops; ++t) {
+    const int oc = d->ops[t].opcode;
+    if (oc < CPUOPS_B200_OP_RELU || oc > CPUOPS_B200_OP_SCALE_PER_COL) {
+      set_error("epilogue opcode %d is not available on s32 accumulators", oc);
+      return CPUOPS_B200_STATUS_UNSUPPORTED;
+    }
+    if (oc >= CPUOPS_B200_OP_BIAS_ADD && !d->ops[t].ptr) return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+  }
+
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (probe_devices() <= 0) {
+    set_error("no sm_100 CUDA device is available; this library has no CPU fallback");
+    return CPUOPS_B200_STATUS_NO_DEVICE;
+  }
+  int device = d->device;
+  if (device < 0) {
+    CUDA_TRY(cudaGetDevice(&device));
+  } else {
+    CUDA_TRY(cudaSetDevice(device));
+  }
+  if (device >= 64) return CPUOPS_B200_STATUS_BAD_DESCRIPTOR;
+  NoAllocDevice* nd = nullptr;
+  if (int rc = noalloc_setup(device, &nd)) return rc;
+  // NULL means the legacy default stream here: creating a stream would be an allocation.
+  cudaStream_t stream = static_cast<cudaStream_t>(d->stream);
+
+  // Operands are used in place, so they must be device memory that TMA can address.
+  const bool a_kmajor = d->a_row_major != 0, b_kmajor = d->b_row_major == 0;
+  const int64_t a_outer = a_kmajor ? m : k, a_inner = a_kmajor ? k : m;
+  const int64_t b_outer = b_kmajor ? n : k, b_inner = b_kmajor ? k : n;
+  if (!is_device_pointer(d->a, d->memory_space) || !is_device_pointer(d->b, d->memory_space) ||
+      !is_device_pointer(d->c, d->memory_space) || !is_device_pointer(d->d, d->memory_space)) {
+    set_error("gemm_i8_noalloc takes device pointers only (staging host memory needs a workspace)");
+    return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+  }
+  if (!tma_addressable(d->a, d->lda, a_outer) || !tma_addressable(d->b, d->ldb, b_outer)) {
+    set_error("gemm_i8_noalloc needs A and B 16-byte aligned with leading dimensions that are "
+              "multiples of 16 (repacking them would need a workspace)");
+    return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+  }
+
+  const int BN = n <= 128 ? 128 : 256;
+  const int k_blocks = (k + 127) / 128;
+  int slices = d->split_k_slices > 0 ? d->split_k_slices : std::min(8, k_blocks);
+  slices = std::max(1, std::min(slices, k_blocks));
+  const size_t need = static_cast<size_t>(slices) * m * n * 4;
+  if (need > CPUOPS_B200_NOALLOC_SCRATCH_BYTES) {
+    set_error("gemm_i8_noalloc: %d slices of a %d x %d s32 result need %zu bytes of scratch; the "
+              "built-in array holds %u (use fewer slices or cpuops_b200_gemm)",
+              slices, m, n, need, static_cast<unsigned>(CPUOPS_B200_NOALLOC_SCRATCH_BYTES));
+    return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+  }
+
+  int32_t* error_word = reinterpret_cast<int32_t*>(nd->scratch);
+  uint32_t* slabs = reinterpret_cast<uint32_t*>(nd->scratch + CPUOPS_B200_NOALLOC_HEADER_BYTES);
+  // The array keeps whatever the previous call left; the error word must start at zero.
+  // (The slabs need no clearing: every slice writes every element it owns.)
+  CUDA_TRY(cudaMemsetAsync(error_word, 0, sizeof(int32_t), stream));
+
+  EpilogueParams epi;
+  memset(&epi, 0, sizeof(epi));
+  epi.D = d->d;
+  epi.C = d->c;
+  epi.d_sr = c_rm ? d->ldd : 1;
+  epi.d_sc = c_rm ? 1 : d->ldd;
+  epi.c_sr = c_rm ? d->ldc : 1;
+  epi.c_sc = c_rm ? 1 : d->ldc;
+  memcpy(&epi.alpha, &d->alpha, 4);
+  memcpy(&epi.beta, &d->beta, 4);
+  epi.beta_nonzero = d->beta.i32 != 0 ? 1 : 0;
+  epi.activation = d->activation == CPUOPS_B200_ACT_RELU ? 1 : 0;
+  epi.n_ops = d->n_ops;
+  for (int t = 0; t < d->n_ops; ++t) {
+    if (d->ops[t].ptr && !is_device_pointer(d->ops[t].ptr, d->memory_space)) {
+      set_error("gemm_i8_noalloc takes device pointers only (epilogue vector %d is host memory)", t);
+      return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+    }
+    epi.ops[t].opcode = d->ops[t].opcode;
+    epi.ops[t].index_by_krow = d->ops[t].opcode == CPUOPS_B200_OP_SCALE_PER_ROW ? 1 : 0;
+    epi.ops[t].ptr = d->ops[t].ptr;
+    memcpy(&epi.ops[t].lo, &d->ops[t].lo, 4);
+    memcpy(&epi.ops[t].hi, &d->ops[t].hi, 4);
+  }
+
+  CUtensorMap tmA, tmB;
+  if (int rc = make_tensor_map(&tmA, d->a, a_inner, a_outer, d->lda, 128)) return rc;
+  if (int rc = make_tensor_map(&tmB, d->b, b_inner, b_outer, d->ldb,
+                               b_kmajor ? static_cast<uint32_t>(BN) : 128u))
+    return rc;
+
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.Mk = m;
+  p.Nk = n;
+  p.K = k;
+  p.m_tiles = (m + kTileM - 1) / kTileM;
+  p.n_tiles = (n + BN - 1) / BN;
+  p.k_blocks = k_blocks;
+  p.slices = slices;
+  p.BN = BN;
+  p.nacc = 2;
+  p.a_mn_major = a_kmajor ? 0 : 1;
+  p.b_mn_major = b_kmajor ? 0 : 1;
+  p.idesc = make_idesc(2 /*s32*/, 0u /*u8*/, 1u /*s8*/, p.a_mn_major, p.b_mn_major, kTileM, BN);
+  p.mode = kModePartial;
+  p.epi = epi;
+  p.ws = slabs;
+  p.ws_slab = static_cast<int64_t>(m) * n;
+  if (epi.d_sr == 1) {  // slab order follows D's contiguous direction
+    p.ws_sr = 1;
+    p.ws_sc = m;
+  } else {
+    p.ws_sr = n;
+    p.ws_sc = 1;
+  }
+  p.error = error_word;
+  const int per_stage = gemm_stage_bytes(BN);
+  int stages = std::min({(nd->smem_optin - 1024 - 256) / per_stage, kMaxStages, std::max(2, k_blocks)});
+  p.stages = stages;
+  const int smem = std::max(gemm_smem_bytes(BN, stages, 0), 120 * 1024);
+  const int64_t total_tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles * p.slices;
+  const unsigned grid = static_cast<unsigned>(std::min<int64_t>(total_tiles, nd->sm_count));
+  gemm_tcgen05_kernel<kKindI8><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, p);
+  g_launches.fetch_add(1);
+  CUDA_TRY(cudaGetLastError());
+  const int64_t total = static_cast<int64_t>(m) * n;
+  const unsigned blocks = static_cast<unsigned>(
+      std::max<int64_t>(1, std::min<int64_t>((total + 255) / 256, static_cast<int64_t>(nd->sm_count) * 16)));
+  reduce_epilogue_kernel<true><<<blocks, 256, 0, stream>>>(epi, slabs, slices, p.ws_slab, m, n, p.ws_sr,
+                                                          p.ws_sc);
+  g_launches.fetch_add(1);
+  CUDA_TRY(cudaGetLastError());
+
+  int32_t device_error = 0;
+  CUDA_TRY(cudaMemcpyAsync(&device_error, error_word, sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+  CUDA_TRY(cudaStreamSynchronize(stream));
+  if (device_error != 0) {
+    set_error("device-side bounded wait timed out (code %d)", device_error);
+    return CPUOPS_B200_STATUS_DEVICE_TIMEOUT;
+  }
+  return CPUOPS_B200_STATUS_SUCCESS;
+}
+
 }  // extern "C"

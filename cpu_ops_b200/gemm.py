@@ -265,6 +265,33 @@ class GemmU8S8S32(_Operator):
         return self._finish(desc, args)
 
 
+    def call_noalloc(self, args: GemmArguments) -> Status:
+        """The same GEMM through ``cpuops_b200_gemm_i8_noalloc``: the two-stage split-k
+        path with its partial sums in the library's built-in scratch array, for hosts
+        that must not trigger a device allocation (a serving process that owns all
+        device memory through its own pool; a latency-critical loop where cudaMalloc
+        would stall the device).  Device operands only; see the C header for limits."""
+        desc = _capi.GemmDesc()
+        desc.kind = _capi.KIND_I8
+        desc.a_format, desc.b_format = _capi.FMT_U8, _capi.FMT_S8
+        ps = args.problem_size
+        desc.m, desc.n, desc.k = int(ps.m), int(ps.n), int(ps.k)
+        desc.a_row_major = int(self.LayoutA.kIsRowMajor)
+        desc.b_row_major = int(self.LayoutB.kIsRowMajor)
+        desc.c_row_major = int(self.LayoutC.kIsRowMajor)
+        desc.a, desc.lda = data_ptr(args.ref_A.data), int(args.ref_A.ld)
+        desc.b, desc.ldb = data_ptr(args.ref_B.data), int(args.ref_B.ld)
+        desc.c, desc.ldc = data_ptr(args.ref_C.data), int(args.ref_C.ld)
+        desc.d, desc.ldd = data_ptr(args.ref_D.data), int(args.ref_D.ld)
+        _fill_epilogue(desc, args.epilogue, True)
+        desc.struct_size = C.sizeof(_capi.GemmDesc)
+        desc.split_k_slices = int(args.split_k_slices)
+        desc.memory_space = self._memory_space
+        desc.stream = self._stream
+        desc.device = self._device
+        return Status(_capi.load().cpuops_b200_gemm_i8_noalloc(C.byref(desc)))
+
+
 class GemmMx(_Operator):
     """gemm::device::GemmMx<StorageA, StorageB, LayoutC> (gemm_mx.h:44-118):
     OCP MX fp8/fp4 elements with one E8M0 scale per 32 k-elements, f32 output."""

@@ -149,6 +149,34 @@ typedef struct cpuops_b200_gemm_desc {
  * Thread-safe. */
 CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* desc);
 
+/* No counterpart in the reference.  u8 x s8 -> s32 GEMM through the two-stage
+ * split-k path for callers that must not allocate device memory: a server that
+ * gave all device memory to its own pool at start-up, or a latency-critical loop
+ * where a cudaMalloc/cudaFree inside the library would stall the whole device.
+ * cpuops_b200_gemm() grows a cached workspace with cudaMalloc when a problem first
+ * needs one; this entry point never calls cudaMalloc, cudaFree or any allocating
+ * routine.  Its split-k partial sums live in a fixed array inside the library image
+ * of CPUOPS_B200_NOALLOC_SCRATCH_BYTES (every GPU that loads the library holds it
+ * until the process exits).
+ *   - Same descriptor and epilogue as cpuops_b200_gemm, kind I8 only, k > 0.
+ *   - All pointers must be device memory; A and B must be 16-byte aligned with
+ *     leading dimensions that are multiples of 16 (nothing can be staged or repacked).
+ *   - split_k_slices: 0 picks min(8, k/128); the slices * m * n * 4 bytes of partial
+ *     sums must fit the array, otherwise CPUOPS_B200_STATUS_INVALID_ARGUMENTS with a
+ *     message naming the size and the limit.
+ *   - stream == NULL means the legacy default stream (no stream is created).
+ *     Synchronous.  FLAG_ASYNC is ignored.
+ *   - The first call on a device looks up the array's device address and sets kernel
+ *     attributes; make that first call before any stream capture begins.
+ *   - All calls share the one array: it keeps the previous call's contents (the
+ *     library clears the one word that must start at zero), and two calls whose
+ *     kernels overlapped on the GPU would race on it.  The call is synchronous and
+ *     serialised inside the library, so this only matters to a caller that loads
+ *     two copies of the library into one process.
+ * Results are bit-identical to cpuops_b200_gemm on the same descriptor. */
+#define CPUOPS_B200_NOALLOC_SCRATCH_BYTES (8u << 20)
+CPUOPS_B200_API int cpuops_b200_gemm_i8_noalloc(const cpuops_b200_gemm_desc* desc);
+
 /* Rewrites a row-major E8M0 scale array (rows x ceil(k/32) entries, leading
  * dimension ld_scales; the addressing of mx_formats.h:280-295, read by
  * mma_policy_mx.h:213,219,242,248) into the tile-ordered layout the tensor
