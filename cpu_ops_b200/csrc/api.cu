@@ -194,6 +194,25 @@ int make_tensor_map(CUtensorMap* tm, const void* base, uint64_t inner, uint64_t 
   return 0;
 }
 
+// 2-D tensor of 32-bit words (C): 32 x 32 boxes, 128-byte swizzled rows.
+int make_tensor_map_words(CUtensorMap* tm, const void* base, uint64_t cols, uint64_t rows,
+                          uint64_t pitch_bytes) {
+  const cuuint64_t dims[2] = {cols, rows};
+  if (rows <= 1) pitch_bytes = (cols * 4 + 15) / 16 * 16;
+  const cuuint64_t strides[1] = {pitch_bytes};
+  const cuuint32_t box[2] = {32, 32};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r =
+      g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box,
+               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled (C) failed with %d", static_cast<int>(r));
+    return CPUOPS_B200_STATUS_CUDA_ERROR;
+  }
+  return 0;
+}
+
 bool tma_addressable(const void* base, int64_t pitch_bytes, int64_t outer) {
   if (reinterpret_cast<uintptr_t>(base) & 15u) return false;
   if (outer > 1 && (pitch_bytes & 15)) return false;
@@ -819,11 +838,19 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
         return CPUOPS_B200_STATUS_CUDA_ERROR;
       }
     }
+    // C through a TMA-fed shared-memory ring when it is row-contiguous in kernel view and
+    // addressable by TMA; otherwise the epilogue loads it directly.
+    CUtensorMap tmC = tmA;
+    if (p.mode == kModeEpilogue && beta_nonzero && epi.c_sc == 1 &&
+        tma_addressable(epi.C, epi.c_sr * 4, Mk) && !getenv("CPUOPS_B200_NO_C_RING")) {
+      if (int rc = make_tensor_map_words(&tmC, epi.C, Nk, Mk, epi.c_sr * 4)) return rc;
+      p.c_ring = 1;
+    }
     p.error = st.error_dev;
     if (const char* dbg = getenv("CPUOPS_B200_DEBUG")) p.debug_flags = atoi(dbg);
     const int sf_stage_bytes = p.sfa_stage_bytes + p.sfb_stage_bytes;
     const int per_stage = gemm_stage_bytes(ch.BN) + sf_stage_bytes;
-    int stages = (st.smem_optin - 1024 - 256) / per_stage;
+    int stages = (st.smem_optin - 1024 - kBarrierBytes - (p.c_ring ? 1024 + kCRingBytes : 0)) / per_stage;
     stages = std::min({stages, kMaxStages, std::max(2, k_blocks)});
     if (stages < 2) {
       set_error("internal: shared memory too small for two stages");
@@ -831,7 +858,7 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
     }
     p.stages = stages;
     // At least 120 KB so that two CTAs never share an SM: each allocates all of tensor memory.
-    const int smem = std::max(gemm_smem_bytes(ch.BN, stages, sf_stage_bytes),
+    const int smem = std::max(gemm_smem_bytes(ch.BN, stages, sf_stage_bytes, p.c_ring),
                               120 * 1024);
     const int64_t total_tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles * p.slices;
     const unsigned grid = static_cast<unsigned>(std::min<int64_t>(total_tiles, st.sm_count));
@@ -842,11 +869,11 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
       CUDA_TRY(cudaEventRecord(ev0, stream));
     }
     if (kind == kKindI8) {
-      gemm_tcgen05_kernel<kKindI8><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, p);
+      gemm_tcgen05_kernel<kKindI8><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, tmC, p);
     } else if (kind == kKindMxf8) {
-      gemm_tcgen05_kernel<kKindMxf8><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, p);
+      gemm_tcgen05_kernel<kKindMxf8><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, tmC, p);
     } else {
-      gemm_tcgen05_kernel<kKindMxf4><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, p);
+      gemm_tcgen05_kernel<kKindMxf4><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, tmC, p);
     }
     g_launches.fetch_add(1);
     CUDA_TRY(cudaGetLastError());
@@ -1103,12 +1130,12 @@ CPUOPS_B200_API int cpuops_b200_gemm_i8_noalloc(const cpuops_b200_gemm_desc* d) 
   }
   p.error = error_word;
   const int per_stage = gemm_stage_bytes(BN);
-  int stages = std::min({(nd->smem_optin - 1024 - 256) / per_stage, kMaxStages, std::max(2, k_blocks)});
+  int stages = std::min({(nd->smem_optin - 1024 - kBarrierBytes) / per_stage, kMaxStages, std::max(2, k_blocks)});
   p.stages = stages;
   const int smem = std::max(gemm_smem_bytes(BN, stages, 0), 120 * 1024);
   const int64_t total_tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles * p.slices;
   const unsigned grid = static_cast<unsigned>(std::min<int64_t>(total_tiles, nd->sm_count));
-  gemm_tcgen05_kernel<kKindI8><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, p);
+  gemm_tcgen05_kernel<kKindI8><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, tmA /*unused: no C ring*/, p);
   g_launches.fetch_add(1);
   CUDA_TRY(cudaGetLastError());
   const int64_t total = static_cast<int64_t>(m) * n;

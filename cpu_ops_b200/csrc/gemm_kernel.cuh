@@ -74,7 +74,8 @@ __device__ __forceinline__ bool aligned16(const void* ptr) {
 // Stores one 32-column chunk of one accumulator row.
 template <bool kInt>
 __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[32], int krow,
-                                            int kcol0, int slice) {
+                                            int kcol0, int slice, const uint32_t* c_smem_row,
+                                            int c_swz) {
   const int ncols = min(32, p.Nk - kcol0);
   if (p.mode == kModePartial) {
     uint32_t* w = static_cast<uint32_t*>(p.ws) + (slice * p.ws_slab + krow * p.ws_sr + kcol0 * p.ws_sc);
@@ -91,7 +92,14 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[3
   }
   const EpilogueParams& e = p.epi;
   uint32_t src[32];
-  if (e.beta_nonzero) {
+  if (c_smem_row != nullptr) {
+    // C chunk prefetched by TMA: this thread's row, 16-byte pieces XOR-swizzled by row & 7
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint4 v = *reinterpret_cast<const uint4*>(c_smem_row + ((j ^ c_swz) << 2));
+      src[4 * j] = v.x; src[4 * j + 1] = v.y; src[4 * j + 2] = v.z; src[4 * j + 3] = v.w;
+    }
+  } else if (e.beta_nonzero) {
     // plain loads: C may alias D
     const uint32_t* c = static_cast<const uint32_t*>(e.C) + (krow * e.c_sr + kcol0 * e.c_sc);
     if (e.c_sc == 1 && ncols == 32 && aligned16(c)) {
@@ -131,7 +139,8 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[3
 template <int KIND>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
-                        const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+                        const __grid_constant__ CUtensorMap tmB,
+                        const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
   constexpr bool kInt = (KIND == kKindI8);
   constexpr bool kMx = !kInt;
 
@@ -148,14 +157,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   // that the operand tiles stay 1024-byte aligned.
   const int sf_stage = p.sfa_stage_bytes + p.sfb_stage_bytes;
   const uint32_t sf_base = smem_base + stages * stage_bytes;
-  const uint32_t bar_base = sf_base + stages * sf_stage;
+  // Optional ring of C chunks (32 rows x 32 columns, 128-byte swizzled), two per epilogue warp.
+  const uint32_t c_base = (sf_base + stages * sf_stage + 1023u) & ~1023u;
+  const uint32_t bar_base = p.c_ring ? c_base + kCRingBytes : sf_base + stages * sf_stage;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
   auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * kMaxStages + b); };
   auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * kMaxStages + 2 + b); };
   const uint32_t drain_bar = bar_base + 8u * (2 * kMaxStages + 4);
+  auto c_full_bar = [&](int w, int b) { return bar_base + 8u * (2 * kMaxStages + 5 + w * 2 + b); };
   uint32_t* tmem_slot =
-      reinterpret_cast<uint32_t*>(smem + (bar_base - smem_base) + 8 * (2 * kMaxStages + 5));
+      reinterpret_cast<uint32_t*>(smem + (bar_base - smem_base) + 8 * (2 * kMaxStages + 5 + 8));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   if (threadIdx.x == 0) {
@@ -168,6 +180,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       mbar_init(acc_empty_bar(b), 4);  // one arrival per epilogue warp
     }
     mbar_init(drain_bar, 1);
+    for (int w = 0; w < 4; ++w)
+      for (int b = 0; b < 2; ++b) mbar_init(c_full_bar(w, b), 1);  // TMA load of one C chunk
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -378,18 +392,35 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const int q = warp & 3;  // the TMEM lane quarter this warp can read
     int it = 0;
     const int nchunks = p.BN / 32;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+    // C ring: two 4 KB buffers per warp, filled by TMA two chunks ahead of their use.
+    const bool ring = p.c_ring != 0;
+    const uint32_t my_c = c_base + static_cast<uint32_t>(q) * 8192u;
+    const uint8_t* my_c_ptr = smem + (my_c - smem_base);
+    uint32_t cq = 0;  // chunks consumed so far by this warp (selects buffer and parity)
+    uint32_t cissued = 0;
+    bool alive = true;
+    for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x, ++it) {
       const TileCoord tc = decode_tile(p, t);
       const int buf = it % nacc;
       const uint32_t acc_ph = static_cast<uint32_t>(it / nacc) & 1u;
+      const int row0 = tc.m_tile * kTileM + q * 32;
+      const int krow = row0 + lane;
+      const int n0 = tc.n_tile * p.BN;
+      if (ring && lane == 0) {
+        // first two chunks of this tile: requested before the accumulator is ready
+        for (int c = 0; c < 2 && c < nchunks; ++c, ++cissued) {
+          const uint32_t b = cissued & 1u;
+          mbar_expect_tx(c_full_bar(q, b), 4096u);
+          tma_load_2d(my_c + b * 4096u, &tmC, c_full_bar(q, b), n0 + c * 32, row0);
+        }
+      }
       const bool ready = mbar_wait_bounded(acc_full_bar(buf), acc_ph, abort_flag);
       if (!__all_sync(0xffffffffu, ready)) {
         if (lane == 0) record_error(p, abort_flag, kErrEpilogueWait);
+        alive = false;
         break;
       }
       tc_fence_after_sync();
-      const int krow = tc.m_tile * kTileM + q * 32 + lane;
-      const int n0 = tc.n_tile * p.BN;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                              static_cast<uint32_t>(buf * p.BN);
       for (int c = 0; c < nchunks; ++c) {
@@ -403,8 +434,35 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           if (lane == 0) mbar_arrive(acc_empty_bar(buf));
         }
         const int kcol0 = n0 + c * 32;
-        if (krow < p.Mk && kcol0 < p.Nk && !(p.debug_flags & 4)) store_chunk<kInt>(p, r, krow, kcol0, tc.slice);
+        const uint32_t* c_row = nullptr;
+        if (ring) {
+          const uint32_t b = cq & 1u;
+          const bool got = mbar_wait_bounded(c_full_bar(q, b), (cq >> 1) & 1u, abort_flag);
+          if (!__all_sync(0xffffffffu, got)) {
+            if (lane == 0) record_error(p, abort_flag, kErrEpilogueWait);
+            alive = false;
+            break;
+          }
+          c_row = reinterpret_cast<const uint32_t*>(my_c_ptr + b * 4096u + lane * 128);
+        }
+        if (krow < p.Mk && kcol0 < p.Nk && !(p.debug_flags & 4))
+          store_chunk<kInt>(p, r, krow, kcol0, tc.slice, c_row, lane & 7);
+        if (ring) {
+          ++cq;
+          __syncwarp();  // every lane has read its row: the buffer may be refilled
+          if (lane == 0 && c + 2 < nchunks) {
+            const uint32_t b = cissued & 1u;
+            mbar_expect_tx(c_full_bar(q, b), 4096u);
+            tma_load_2d(my_c + b * 4096u, &tmC, c_full_bar(q, b), n0 + (c + 2) * 32, row0);
+            ++cissued;
+          }
+        }
       }
+    }
+    if (ring && *abort_flag != 0 && lane == 0) {
+      // let C chunks that were requested but never consumed land before the CTA exits
+      int dummy = 0;
+      for (; cq < cissued; ++cq) mbar_wait_bounded(c_full_bar(q, cq & 1u), (cq >> 1) & 1u, &dummy);
     }
   }
 

@@ -73,15 +73,18 @@ struct GemmParams {
   const uint8_t* sfa;
   const uint8_t* sfb;
   int32_t sfa_stage_bytes, sfb_stage_bytes;  // per k-block
+  int32_t c_ring;           // 1: C tiles are prefetched by TMA into a shared-memory ring
   int32_t* error;           // device error word
   int32_t debug_flags;      // experiments only (CPUOPS_B200_DEBUG)
 };
 
 // Shared-memory footprint of one launch of the GEMM kernel.
 __host__ __device__ inline int gemm_stage_bytes(int BN) { return kTileM * 128 + BN * 128; }
-__host__ __device__ inline int gemm_smem_bytes(int BN, int stages, int sf_stage_bytes) {
+constexpr int kCRingBytes = 4 /*epilogue warps*/ * 2 /*buffers*/ * 4096;  // 32 rows x 32 cols x 4 B each
+constexpr int kBarrierBytes = 512;  // barriers, TMEM slot, abort flag
+__host__ __device__ inline int gemm_smem_bytes(int BN, int stages, int sf_stage_bytes, int c_ring = 0) {
   return 1024 /*alignment slack*/ + stages * (gemm_stage_bytes(BN) + sf_stage_bytes) +
-         256 /*barriers, TMEM slot, abort flag*/;
+         (c_ring ? 1024 + kCRingBytes : 0) + kBarrierBytes;
 }
 
 }  // namespace b200

@@ -99,6 +99,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
       : "memory");
 }
 
+// Asks the memory system to bring a 2-D box into L2 (no shared-memory destination).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* tm, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(
+                   reinterpret_cast<uint64_t>(tm)),
+               "r"(x), "r"(y)
+               : "memory");
+}
+
 // Untiled bulk copy global -> shared (16-byte aligned addresses, size % 16 == 0).
 __device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* gmem, uint32_t bytes,
                                           uint32_t bar) {
