@@ -23,6 +23,7 @@
 
 #include "../../include/cpu_ops_b200.h"
 #include "aux_kernels.cuh"
+#include "decode_kernel.cuh"
 #include "gemm_kernel.cuh"
 #include "gemm_params.h"
 
@@ -56,6 +57,8 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+constexpr int kDecodeCounterSlots = 1 << 16;
+
 struct DeviceState {
   bool ready = false;
   int device = -1;
@@ -64,6 +67,7 @@ struct DeviceState {
   cudaStream_t stream = nullptr;  // the library's own stream
   int32_t* error_dev = nullptr;   // device error word
   int32_t* error_host = nullptr;  // pinned mirror
+  int32_t* decode_counters = nullptr;  // per-tile arrival counters of the decode kernel (self-resetting)
   // grow-only workspaces, one per stream that ever called in
   struct Workspace {
     void* ptr = nullptr;
@@ -75,6 +79,8 @@ struct DeviceState {
 // Optional timing of the tensor-core kernel alone (events on the launching stream).
 bool g_profile = false;
 std::vector<std::pair<cudaEvent_t, cudaEvent_t>> g_profile_events;
+
+unsigned long long* g_clk_buf = nullptr;  // experiments only (CPUOPS_B200_CLK)
 
 std::mutex g_mu;  // serialises calls (the CPU library serialises on its pool mutex too)
 DeviceState g_dev[64];
@@ -125,6 +131,8 @@ int init_device(int device, DeviceState** out) {
     CUDA_TRY(cudaStreamCreateWithFlags(&st.stream, cudaStreamNonBlocking));
     CUDA_TRY(cudaMalloc(&st.error_dev, sizeof(int32_t)));
     CUDA_TRY(cudaMemset(st.error_dev, 0, sizeof(int32_t)));
+    CUDA_TRY(cudaMalloc(&st.decode_counters, kDecodeCounterSlots * sizeof(int32_t)));
+    CUDA_TRY(cudaMemset(st.decode_counters, 0, kDecodeCounterSlots * sizeof(int32_t)));
     CUDA_TRY(cudaMallocHost(&st.error_host, sizeof(int32_t)));
     *st.error_host = 0;
     if (!g_encode) {
@@ -142,6 +150,10 @@ int init_device(int device, DeviceState** out) {
     CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindMxf8>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
     CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindMxf4>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
+    CUDA_TRY(cudaFuncSetAttribute(decode_gemm_kernel<kKindMxf8>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
+    CUDA_TRY(cudaFuncSetAttribute(decode_gemm_kernel<kKindMxf4>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
     st.ready = true;
   } else {
@@ -386,6 +398,15 @@ CPUOPS_B200_API int cpuops_b200_stream_status(void* stream) {
   return 0;
 }
 
+// Experiments only, not declared in the public header: {SM cycles, ns} of CTA 0 of the
+// last GEMM kernel when CPUOPS_B200_CLK is set.
+CPUOPS_B200_API int cpuops_b200_debug_clock(unsigned long long* out) {
+  if (!g_clk_buf || !out) return 1;
+  cudaDeviceSynchronize();
+  for (int i = 0; i < 8; ++i) out[i] = g_clk_buf[i];
+  return 0;
+}
+
 CPUOPS_B200_API int cpuops_b200_profile(int enable) {
   std::lock_guard<std::mutex> lk(g_mu);
   g_profile = enable != 0;
@@ -575,6 +596,18 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
     }
   }
 
+  // Small-m MX problems take the single-launch decode kernel (raw scales, no re-layout
+  // pass, no reduction pass) unless the caller forces a slice count.
+  const bool use_decode = is_mx && k > 0 && m <= 64 && n >= 128 && d->split_k_slices == 0 &&
+                          d->tile_n == 0 && (n + 127) / 128 <= kDecodeCounterSlots &&
+                          !getenv("CPUOPS_B200_NO_DECODE");
+  const int decode_bn = m <= 32 ? 32 : 64;
+  if (use_decode) {
+    ch.swap = true;
+    ch.BN = decode_bn;
+    ch.slices = 1;
+  }
+
   // ---- workspace plan ------------------------------------------------------------------
   Plan plan;
   const int64_t c_outer = c_rm ? m : n, c_inner = c_rm ? n : m;
@@ -627,7 +660,10 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
   if (k > 0) {
     Mk = ch.swap ? n : m;
     Nk = ch.swap ? m : n;
-    if (is_mx) {
+    if (use_decode) {
+      bps = fp4_a ? 8 : 4;
+      off_ws = plan.take(static_cast<size_t>((n + 127) / 128) * kDecodeMaxSegments * decode_bn * kTileM * 4);
+    } else if (is_mx) {
       bps = fp4_a ? 8 : 4;
       sfa_bytes = cpuops_b200_scale_layout_bytes(Mk, k, kTileM, bps);
       sfb_bytes = cpuops_b200_scale_layout_bytes(Nk, k, ch.BN, bps);
@@ -762,6 +798,69 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
     }
     g_launches.fetch_add(1);
     CUDA_TRY(cudaGetLastError());
+  } else if (use_decode) {
+    // ---- decode-shaped MX GEMM: one launch ---------------------------------------------------
+    // kernel view: weights = caller's B (n rows of k), activations = caller's A (m rows of k)
+    CUtensorMap tmW, tmX;
+    if (int rc = make_tensor_map(&tmW, b_ptr, B.inner_bytes, B.outer, b_pitch_dev, 128)) return rc;
+    if (int rc = make_tensor_map(&tmX, a_ptr, A.inner_bytes, A.outer, a_pitch_dev,
+                                 static_cast<uint32_t>(decode_bn)))
+      return rc;
+    DecodeParams dp;
+    memset(&dp, 0, sizeof(dp));
+    dp.rows_w = n;
+    dp.rows_x = m;
+    dp.K = k;
+    dp.n_tiles = (n + kTileM - 1) / kTileM;
+    dp.k_blocks = k_blocks;
+    dp.units = dp.n_tiles * dp.k_blocks;
+    dp.BN = decode_bn;
+    dp.bps = bps;
+    dp.scale_blocks = (k + 31) / 32;
+    if (kind == kKindMxf8) {
+      dp.idesc = make_idesc_block_scaled(d->b_format == CPUOPS_B200_FMT_E5M2 ? 1u : 0u,
+                                         d->a_format == CPUOPS_B200_FMT_E5M2 ? 1u : 0u, kTileM, decode_bn);
+    } else {
+      dp.idesc = make_idesc_block_scaled(1u, 1u, kTileM, decode_bn);
+    }
+    dp.sw = sb_ptr;
+    dp.ldsw = d->ld_scales_b;
+    dp.sx = sa_ptr;
+    dp.ldsx = d->ld_scales_a;
+    dp.epi = epi;  // already in kernel view (swap == true)
+    dp.slabs = reinterpret_cast<uint32_t*>(wsp + off_ws);
+    dp.counters = st.decode_counters;
+    dp.error = st.error_dev;
+    if (getenv("CPUOPS_B200_CLK")) {
+      if (!g_clk_buf) cudaMallocManaged(&g_clk_buf, 64);
+      dp.clk_dbg = g_clk_buf;
+    }
+    const int sf_kb = (bps / 4) * 1024;
+    const int stage_bytes = kTileM * 128 + decode_bn * 128;
+    const int sf_smem = 2 * kSfChunkKb * sf_kb;
+    dp.stages = std::min({(st.smem_optin - 1024 - kBarrierBytes - sf_smem) / stage_bytes, kMaxStages,
+                          std::max(2, dp.units)});
+    const int smem = std::max(1024 + dp.stages * stage_bytes + sf_smem + kBarrierBytes, 120 * 1024);
+    // every CTA gets at least half a tile's k so that a tile is shared by at most 3 CTAs
+    const int min_units = std::max(1, (dp.k_blocks + 1) / 2);
+    const unsigned grid = static_cast<unsigned>(std::max(1, std::min(st.sm_count, dp.units / min_units)));
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    if (g_profile) {
+      CUDA_TRY(cudaEventCreate(&ev0));
+      CUDA_TRY(cudaEventCreate(&ev1));
+      CUDA_TRY(cudaEventRecord(ev0, stream));
+    }
+    if (kind == kKindMxf8) {
+      decode_gemm_kernel<kKindMxf8><<<grid, kDecodeThreads, smem, stream>>>(tmW, tmX, dp);
+    } else {
+      decode_gemm_kernel<kKindMxf4><<<grid, kDecodeThreads, smem, stream>>>(tmW, tmX, dp);
+    }
+    g_launches.fetch_add(1);
+    CUDA_TRY(cudaGetLastError());
+    if (g_profile) {
+      CUDA_TRY(cudaEventRecord(ev1, stream));
+      g_profile_events.emplace_back(ev0, ev1);
+    }
   } else {
     // ---- scales -> tile-ordered layout (MX) ------------------------------------------------
     const uint8_t* ak_ptr = swap ? b_ptr : a_ptr;  // kernel-view A (M side), B (N side)
@@ -848,6 +947,10 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
     }
     p.error = st.error_dev;
     if (const char* dbg = getenv("CPUOPS_B200_DEBUG")) p.debug_flags = atoi(dbg);
+    if (getenv("CPUOPS_B200_CLK")) {
+      if (!g_clk_buf) cudaMallocManaged(&g_clk_buf, 64);
+      p.clk_dbg = g_clk_buf;
+    }
     const int sf_stage_bytes = p.sfa_stage_bytes + p.sfb_stage_bytes;
     const int per_stage = gemm_stage_bytes(ch.BN) + sf_stage_bytes;
     int stages = (st.smem_optin - 1024 - kBarrierBytes - (p.c_ring ? 1024 + kCRingBytes : 0)) / per_stage;
@@ -907,6 +1010,7 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
     set_error("device-side bounded wait timed out (code %d)", *st.error_host);
     *st.error_host = 0;
     cudaMemsetAsync(st.error_dev, 0, sizeof(int32_t), stream);
+    cudaMemsetAsync(st.decode_counters, 0, kDecodeCounterSlots * sizeof(int32_t), stream);
     cudaStreamSynchronize(stream);
     return CPUOPS_B200_STATUS_DEVICE_TIMEOUT;
   }

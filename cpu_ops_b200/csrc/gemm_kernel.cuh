@@ -200,6 +200,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
   const int total_tiles = p.m_tiles * p.n_tiles * p.slices;
   const int nacc = p.nacc;
+  long long dbg_c0 = 0;
+  uint64_t dbg_t0 = 0;
+  if (p.clk_dbg != nullptr && blockIdx.x == 0 && threadIdx.x == 64) {
+    dbg_c0 = clock64();
+    dbg_t0 = global_timer_ns();
+  }
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -314,24 +320,31 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const uint32_t sf_lo0 = static_cast<uint32_t>(sf_hi64) | (sf_base >> 4);
       const uint32_t full0 = full_bar(0), empty0 = empty_bar(0);
 
+      const bool dbg = p.clk_dbg != nullptr && blockIdx.x == 0;
+      long long dbg_wait_acc = 0, dbg_wait_full = 0;
+      const long long dbg_start = dbg ? clock64() : 0;
       int s = 0, buf = 0;
       uint32_t ph = 0, acc_ph = 0;
       uint32_t a_lo = a_lo0, b_lo = b_lo0, full_addr = full0, empty_addr = empty0, sf_lo = sf_lo0;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const TileCoord tc = decode_tile(p, t);
+        long long tw0 = dbg ? clock64() : 0;
         if (!mbar_wait_bounded(acc_empty_bar(buf), acc_ph ^ 1u, abort_flag)) {
           record_error(p, abort_flag, kErrMmaWaitAcc);
           break;
         }
+        if (dbg) dbg_wait_acc += clock64() - tw0;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * p.BN);
         uint32_t accumulate = 0;
         for (int i = 0; i < tc.nkb; ++i) {
+          tw0 = dbg ? clock64() : 0;
           if (!mbar_wait_bounded(full_addr, ph, abort_flag)) {
             record_error(p, abort_flag, kErrMmaWaitFull);
             ok = false;
             break;
           }
+          if (dbg) dbg_wait_full += clock64() - tw0;
           tc_fence_after_sync();
           if constexpr (kMx) {
             // The k-block's scale factors: shared -> tensor memory.  Issued by the same
@@ -385,6 +398,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       tc_commit(drain_bar);
       int dummy = 0;
       if (!mbar_wait_bounded(drain_bar, 0, &dummy)) record_error(p, abort_flag, kErrDrainWait);
+      if (dbg) {
+        p.clk_dbg[2] = static_cast<unsigned long long>(clock64() - dbg_start);
+        p.clk_dbg[3] = static_cast<unsigned long long>(dbg_wait_full);
+        p.clk_dbg[4] = static_cast<unsigned long long>(dbg_wait_acc);
+      }
     }
     __syncwarp();
   } else {
@@ -399,6 +417,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     uint32_t cq = 0;  // chunks consumed so far by this warp (selects buffer and parity)
     uint32_t cissued = 0;
     bool alive = true;
+    const bool edbg = p.clk_dbg != nullptr && blockIdx.x == 0 && warp == 2 && lane == 0;
+    long long edbg_wait = 0;
+    const long long edbg_start = edbg ? clock64() : 0;
     for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x, ++it) {
       const TileCoord tc = decode_tile(p, t);
       const int buf = it % nacc;
@@ -414,12 +435,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           tma_load_2d(my_c + b * 4096u, &tmC, c_full_bar(q, b), n0 + c * 32, row0);
         }
       }
+      const long long te0 = edbg ? clock64() : 0;
       const bool ready = mbar_wait_bounded(acc_full_bar(buf), acc_ph, abort_flag);
       if (!__all_sync(0xffffffffu, ready)) {
         if (lane == 0) record_error(p, abort_flag, kErrEpilogueWait);
         alive = false;
         break;
       }
+      if (edbg) edbg_wait += clock64() - te0;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                              static_cast<uint32_t>(buf * p.BN);
@@ -459,6 +482,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
       }
     }
+    if (edbg) {
+      p.clk_dbg[5] = static_cast<unsigned long long>(clock64() - edbg_start);
+      p.clk_dbg[6] = static_cast<unsigned long long>(edbg_wait);
+    }
     if (ring && *abort_flag != 0 && lane == 0) {
       // let C chunks that were requested but never consumed land before the CTA exits
       int dummy = 0;
@@ -466,6 +493,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
   }
 
+  if (p.clk_dbg != nullptr && blockIdx.x == 0 && threadIdx.x == 64) {
+    p.clk_dbg[0] = static_cast<unsigned long long>(clock64() - dbg_c0);
+    p.clk_dbg[1] = global_timer_ns() - dbg_t0;
+  }
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);

@@ -76,6 +76,7 @@ struct GemmParams {
   int32_t c_ring;           // 1: C tiles are prefetched by TMA into a shared-memory ring
   int32_t* error;           // device error word
   int32_t debug_flags;      // experiments only (CPUOPS_B200_DEBUG)
+  unsigned long long* clk_dbg;  // experiments only: {SM cycles, nanoseconds} of CTA 0
 };
 
 // Shared-memory footprint of one launch of the GEMM kernel.
