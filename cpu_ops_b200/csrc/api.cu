@@ -23,7 +23,6 @@
 
 #include "../../include/cpu_ops_b200.h"
 #include "aux_kernels.cuh"
-#include "decode_kernel.cuh"
 #include "gemm_kernel.cuh"
 #include "gemm_params.h"
 
@@ -57,7 +56,6 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-constexpr int kDecodeCounterSlots = 1 << 16;
 
 struct DeviceState {
   bool ready = false;
@@ -67,7 +65,6 @@ struct DeviceState {
   cudaStream_t stream = nullptr;  // the library's own stream
   int32_t* error_dev = nullptr;   // device error word
   int32_t* error_host = nullptr;  // pinned mirror
-  int32_t* decode_counters = nullptr;  // per-tile arrival counters of the decode kernel (self-resetting)
   // grow-only workspaces, one per stream that ever called in
   struct Workspace {
     void* ptr = nullptr;
@@ -131,8 +128,6 @@ int init_device(int device, DeviceState** out) {
     CUDA_TRY(cudaStreamCreateWithFlags(&st.stream, cudaStreamNonBlocking));
     CUDA_TRY(cudaMalloc(&st.error_dev, sizeof(int32_t)));
     CUDA_TRY(cudaMemset(st.error_dev, 0, sizeof(int32_t)));
-    CUDA_TRY(cudaMalloc(&st.decode_counters, kDecodeCounterSlots * sizeof(int32_t)));
-    CUDA_TRY(cudaMemset(st.decode_counters, 0, kDecodeCounterSlots * sizeof(int32_t)));
     CUDA_TRY(cudaMallocHost(&st.error_host, sizeof(int32_t)));
     *st.error_host = 0;
     if (!g_encode) {
@@ -150,10 +145,6 @@ int init_device(int device, DeviceState** out) {
     CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindMxf8>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
     CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindMxf4>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
-    CUDA_TRY(cudaFuncSetAttribute(decode_gemm_kernel<kKindMxf8>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
-    CUDA_TRY(cudaFuncSetAttribute(decode_gemm_kernel<kKindMxf4>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
     st.ready = true;
   } else {
@@ -182,7 +173,45 @@ int ensure_workspace(DeviceState& st, cudaStream_t stream, size_t bytes, uint8_t
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+// Experiment switches, read from the environment once.
+struct EnvSwitches {
+  bool no_c_ring = getenv("CPUOPS_B200_NO_C_RING") != nullptr;
+  bool clk = getenv("CPUOPS_B200_CLK") != nullptr;
+  int debug_flags = getenv("CPUOPS_B200_DEBUG") ? atoi(getenv("CPUOPS_B200_DEBUG")) : 0;
+};
+const EnvSwitches& env_switches() {
+  static const EnvSwitches e;
+  return e;
+}
+
 // ---- tensor maps --------------------------------------------------------------
+
+// A tensor map is a pure function of its encode arguments, and a caller that repeats
+// a GEMM on the same buffers (a decode loop) asks for the same few maps again and
+// again: a small direct-mapped cache saves the driver call (about a microsecond each).
+// Guarded by g_mu like the rest of the call.
+struct TensorMapKey {
+  uint64_t base, d0, d1, pitch;
+  uint32_t box1, words;
+  bool operator==(const TensorMapKey& o) const {
+    return base == o.base && d0 == o.d0 && d1 == o.d1 && pitch == o.pitch && box1 == o.box1 &&
+           words == o.words;
+  }
+};
+struct TensorMapSlot {
+  bool valid = false;
+  TensorMapKey key;
+  CUtensorMap map;
+};
+constexpr int kTensorMapSlots = 64;
+TensorMapSlot g_tm_cache[kTensorMapSlots];
+
+TensorMapSlot& tensor_map_slot(const TensorMapKey& k) {
+  uint64_t h = k.base * 0x9E3779B97F4A7C15ull;
+  h ^= (k.d0 + 0x632BE59BD9B4E019ull) * 0xC2B2AE3D27D4EB4Full;
+  h ^= (k.d1 * 31 + k.pitch * 17 + k.box1 * 7 + k.words) * 0x165667B19E3779F9ull;
+  return g_tm_cache[(h >> 32) % kTensorMapSlots];
+}
 
 // 2-D byte tensor: `inner` contiguous bytes per row, `outer` rows `pitch` bytes
 // apart; 128-byte swizzled boxes of box_outer rows; out-of-range reads are zero.
@@ -190,6 +219,12 @@ int make_tensor_map(CUtensorMap* tm, const void* base, uint64_t inner, uint64_t 
                     uint64_t pitch, uint32_t box_outer) {
   const cuuint64_t dims[2] = {inner, outer};
   if (outer <= 1) pitch = (inner + 15) / 16 * 16;  // a single row: the pitch is never used
+  const TensorMapKey key{reinterpret_cast<uint64_t>(base), inner, outer, pitch, box_outer, 0u};
+  TensorMapSlot& slot = tensor_map_slot(key);
+  if (slot.valid && slot.key == key) {
+    *tm = slot.map;
+    return 0;
+  }
   const cuuint64_t strides[1] = {pitch};
   const cuuint32_t box[2] = {128, box_outer};
   const cuuint32_t estr[2] = {1, 1};
@@ -203,6 +238,9 @@ int make_tensor_map(CUtensorMap* tm, const void* base, uint64_t inner, uint64_t 
               (unsigned long long)pitch, box_outer);
     return CPUOPS_B200_STATUS_CUDA_ERROR;
   }
+  slot.valid = true;
+  slot.key = key;
+  slot.map = *tm;
   return 0;
 }
 
@@ -211,6 +249,12 @@ int make_tensor_map_words(CUtensorMap* tm, const void* base, uint64_t cols, uint
                           uint64_t pitch_bytes) {
   const cuuint64_t dims[2] = {cols, rows};
   if (rows <= 1) pitch_bytes = (cols * 4 + 15) / 16 * 16;
+  const TensorMapKey key{reinterpret_cast<uint64_t>(base), cols, rows, pitch_bytes, 32u, 1u};
+  TensorMapSlot& slot = tensor_map_slot(key);
+  if (slot.valid && slot.key == key) {
+    *tm = slot.map;
+    return 0;
+  }
   const cuuint64_t strides[1] = {pitch_bytes};
   const cuuint32_t box[2] = {32, 32};
   const cuuint32_t estr[2] = {1, 1};
@@ -222,6 +266,9 @@ int make_tensor_map_words(CUtensorMap* tm, const void* base, uint64_t cols, uint
     set_error("cuTensorMapEncodeTiled (C) failed with %d", static_cast<int>(r));
     return CPUOPS_B200_STATUS_CUDA_ERROR;
   }
+  slot.valid = true;
+  slot.key = key;
+  slot.map = *tm;
   return 0;
 }
 
@@ -277,15 +324,15 @@ int pick_bn_for_small(int nk) {
   return 256;
 }
 
-// Cost of one configuration in MMA-pipe cycles (relative): waves of tiles over
-// the SMs times the per-tile time, where a k-block costs the larger of the MMA
-// issue time (BN/2 cycles for 128 x BN x 32 B) and the shared-memory read time
-// ((128 + BN) * 32 B at 128 B/clk); a single accumulator buffer cannot overlap
-// the epilogue with the next mainloop.
+// Modelled cycles of one CTA's share of the problem for N tile `BN`.  Measured on
+// B200: with one CTA per SM the k loop is bound by the L2 -> shared-memory feed
+// (about 64 bytes per clock per SM) rather than by the MMA itself (BN / 2 clocks per
+// 32-byte k step), so a k-block costs 2 * (128 + BN) clocks; the epilogue overlaps
+// the next tile's k loop only when there are two accumulator buffers.
 double config_cost(int Mk, int Nk, int k_blocks, int BN, int nacc, int sms, bool beta) {
   const int64_t tiles = static_cast<int64_t>((Mk + 127) / 128) * ((Nk + BN - 1) / BN);
   const int64_t waves = (tiles + sms - 1) / sms;
-  const double kblock = 4.0 * std::max(BN / 2.0, (128.0 + BN) / 4.0);
+  const double kblock = std::max(2.0 * BN, 2.0 * (128.0 + BN));
   const double epi = 128.0 * BN * (beta ? 8.0 : 4.0) / 20.0;  // ~20 B/clk/SM of HBM
   const double tile = k_blocks * kblock + (nacc == 1 ? epi : 0.15 * epi);
   return static_cast<double>(waves) * tile;
@@ -351,10 +398,10 @@ static ScaleLayout make_scale_layout(int rows, int k, int ld, int tile_rows, int
 // Re-lays-out one scale array, or two (src1 != nullptr) in a single launch.
 static int launch_relayout(const void* src0, void* dst0, const ScaleLayout& L0, const void* src1,
                            void* dst1, const ScaleLayout& L1, cudaStream_t stream) {
-  int64_t atoms = static_cast<int64_t>(L0.tiles) * L0.stages * L0.ka * L0.nb128;
-  if (src1) atoms += static_cast<int64_t>(L1.tiles) * L1.stages * L1.ka * L1.nb128;
-  const int threads = 256;
-  const int64_t blocks = std::min<int64_t>((atoms * 32 + threads - 1) / threads, 148 * 16);
+  int64_t items = relayout_work_items(L0);  // one warp each
+  if (src1) items += relayout_work_items(L1);
+  const int threads = 128;
+  const int64_t blocks = std::min<int64_t>((items * 32 + threads - 1) / threads, 148 * 16);
   relayout_scales_kernel<<<static_cast<unsigned>(std::max<int64_t>(blocks, 1)), threads, 0, stream>>>(
       static_cast<const uint8_t*>(src0), static_cast<uint8_t*>(dst0), L0,
       static_cast<const uint8_t*>(src1), static_cast<uint8_t*>(dst1), L1);
@@ -403,7 +450,8 @@ CPUOPS_B200_API int cpuops_b200_stream_status(void* stream) {
 CPUOPS_B200_API int cpuops_b200_debug_clock(unsigned long long* out) {
   if (!g_clk_buf || !out) return 1;
   cudaDeviceSynchronize();
-  for (int i = 0; i < 8; ++i) out[i] = g_clk_buf[i];
+  // [8],[9]: first CTA start / last CTA end (ns)
+  cudaMemcpy(out, g_clk_buf, 10 * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
   return 0;
 }
 
@@ -557,9 +605,9 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
       ch.BN = bk_role_mn ? 128 : pick_bn_for_small(Nk);
     } else {
       double best = 1e300;
-      for (int bn : {256, 192, 128}) {
-        if (bk_role_mn && bn == 192) continue;
-        const int nacc = (is_mx && bn == 256) ? 1 : 2;
+      for (int bn : {256, 224, 192, 160, 128}) {
+        if (bk_role_mn && bn % 128 != 0) continue;
+        const int nacc = (is_mx && bn > 224) ? 1 : 2;
         const double c = config_cost(Mk, Nk, k_blocks, bn, nacc, st.sm_count, beta_nonzero);
         if (c < best) {
           best = c;
@@ -594,18 +642,6 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
         }
       }
     }
-  }
-
-  // Small-m MX problems take the single-launch decode kernel (raw scales, no re-layout
-  // pass, no reduction pass) unless the caller forces a slice count.
-  const bool use_decode = is_mx && k > 0 && m <= 64 && n >= 128 && d->split_k_slices == 0 &&
-                          d->tile_n == 0 && (n + 127) / 128 <= kDecodeCounterSlots &&
-                          !getenv("CPUOPS_B200_NO_DECODE");
-  const int decode_bn = m <= 32 ? 32 : 64;
-  if (use_decode) {
-    ch.swap = true;
-    ch.BN = decode_bn;
-    ch.slices = 1;
   }
 
   // ---- workspace plan ------------------------------------------------------------------
@@ -660,10 +696,7 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
   if (k > 0) {
     Mk = ch.swap ? n : m;
     Nk = ch.swap ? m : n;
-    if (use_decode) {
-      bps = fp4_a ? 8 : 4;
-      off_ws = plan.take(static_cast<size_t>((n + 127) / 128) * kDecodeMaxSegments * decode_bn * kTileM * 4);
-    } else if (is_mx) {
+    if (is_mx) {
       bps = fp4_a ? 8 : 4;
       sfa_bytes = cpuops_b200_scale_layout_bytes(Mk, k, kTileM, bps);
       sfb_bytes = cpuops_b200_scale_layout_bytes(Nk, k, ch.BN, bps);
@@ -798,69 +831,6 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
     }
     g_launches.fetch_add(1);
     CUDA_TRY(cudaGetLastError());
-  } else if (use_decode) {
-    // ---- decode-shaped MX GEMM: one launch ---------------------------------------------------
-    // kernel view: weights = caller's B (n rows of k), activations = caller's A (m rows of k)
-    CUtensorMap tmW, tmX;
-    if (int rc = make_tensor_map(&tmW, b_ptr, B.inner_bytes, B.outer, b_pitch_dev, 128)) return rc;
-    if (int rc = make_tensor_map(&tmX, a_ptr, A.inner_bytes, A.outer, a_pitch_dev,
-                                 static_cast<uint32_t>(decode_bn)))
-      return rc;
-    DecodeParams dp;
-    memset(&dp, 0, sizeof(dp));
-    dp.rows_w = n;
-    dp.rows_x = m;
-    dp.K = k;
-    dp.n_tiles = (n + kTileM - 1) / kTileM;
-    dp.k_blocks = k_blocks;
-    dp.units = dp.n_tiles * dp.k_blocks;
-    dp.BN = decode_bn;
-    dp.bps = bps;
-    dp.scale_blocks = (k + 31) / 32;
-    if (kind == kKindMxf8) {
-      dp.idesc = make_idesc_block_scaled(d->b_format == CPUOPS_B200_FMT_E5M2 ? 1u : 0u,
-                                         d->a_format == CPUOPS_B200_FMT_E5M2 ? 1u : 0u, kTileM, decode_bn);
-    } else {
-      dp.idesc = make_idesc_block_scaled(1u, 1u, kTileM, decode_bn);
-    }
-    dp.sw = sb_ptr;
-    dp.ldsw = d->ld_scales_b;
-    dp.sx = sa_ptr;
-    dp.ldsx = d->ld_scales_a;
-    dp.epi = epi;  // already in kernel view (swap == true)
-    dp.slabs = reinterpret_cast<uint32_t*>(wsp + off_ws);
-    dp.counters = st.decode_counters;
-    dp.error = st.error_dev;
-    if (getenv("CPUOPS_B200_CLK")) {
-      if (!g_clk_buf) cudaMallocManaged(&g_clk_buf, 64);
-      dp.clk_dbg = g_clk_buf;
-    }
-    const int sf_kb = (bps / 4) * 1024;
-    const int stage_bytes = kTileM * 128 + decode_bn * 128;
-    const int sf_smem = 2 * kSfChunkKb * sf_kb;
-    dp.stages = std::min({(st.smem_optin - 1024 - kBarrierBytes - sf_smem) / stage_bytes, kMaxStages,
-                          std::max(2, dp.units)});
-    const int smem = std::max(1024 + dp.stages * stage_bytes + sf_smem + kBarrierBytes, 120 * 1024);
-    // every CTA gets at least half a tile's k so that a tile is shared by at most 3 CTAs
-    const int min_units = std::max(1, (dp.k_blocks + 1) / 2);
-    const unsigned grid = static_cast<unsigned>(std::max(1, std::min(st.sm_count, dp.units / min_units)));
-    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
-    if (g_profile) {
-      CUDA_TRY(cudaEventCreate(&ev0));
-      CUDA_TRY(cudaEventCreate(&ev1));
-      CUDA_TRY(cudaEventRecord(ev0, stream));
-    }
-    if (kind == kKindMxf8) {
-      decode_gemm_kernel<kKindMxf8><<<grid, kDecodeThreads, smem, stream>>>(tmW, tmX, dp);
-    } else {
-      decode_gemm_kernel<kKindMxf4><<<grid, kDecodeThreads, smem, stream>>>(tmW, tmX, dp);
-    }
-    g_launches.fetch_add(1);
-    CUDA_TRY(cudaGetLastError());
-    if (g_profile) {
-      CUDA_TRY(cudaEventRecord(ev1, stream));
-      g_profile_events.emplace_back(ev0, ev1);
-    }
   } else {
     // ---- scales -> tile-ordered layout (MX) ------------------------------------------------
     const uint8_t* ak_ptr = swap ? b_ptr : a_ptr;  // kernel-view A (M side), B (N side)
@@ -941,14 +911,16 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
     // addressable by TMA; otherwise the epilogue loads it directly.
     CUtensorMap tmC = tmA;
     if (p.mode == kModeEpilogue && beta_nonzero && epi.c_sc == 1 &&
-        tma_addressable(epi.C, epi.c_sr * 4, Mk) && !getenv("CPUOPS_B200_NO_C_RING")) {
+        tma_addressable(epi.C, epi.c_sr * 4, Mk) && !env_switches().no_c_ring) {
       if (int rc = make_tensor_map_words(&tmC, epi.C, Nk, Mk, epi.c_sr * 4)) return rc;
       p.c_ring = 1;
     }
     p.error = st.error_dev;
-    if (const char* dbg = getenv("CPUOPS_B200_DEBUG")) p.debug_flags = atoi(dbg);
-    if (getenv("CPUOPS_B200_CLK")) {
-      if (!g_clk_buf) cudaMallocManaged(&g_clk_buf, 64);
+    p.debug_flags = env_switches().debug_flags;
+    if (env_switches().clk) {
+      if (!g_clk_buf) cudaMalloc(&g_clk_buf, 128);
+      cudaMemsetAsync(g_clk_buf + 8, 0xFF, 8, stream);
+      cudaMemsetAsync(g_clk_buf + 9, 0, 8, stream);
       p.clk_dbg = g_clk_buf;
     }
     const int sf_stage_bytes = p.sfa_stage_bytes + p.sfb_stage_bytes;
@@ -973,10 +945,26 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
     }
     if (kind == kKindI8) {
       gemm_tcgen05_kernel<kKindI8><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, tmC, p);
-    } else if (kind == kKindMxf8) {
-      gemm_tcgen05_kernel<kKindMxf8><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, tmC, p);
     } else {
-      gemm_tcgen05_kernel<kKindMxf4><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, tmC, p);
+      // MX: the scale re-layout kernel is the launch just before this one.  Programmatic
+      // stream serialization lets this kernel's CTAs start (barriers, tensor memory,
+      // descriptor prefetch) while that one is still running; the producer thread waits
+      // for it before the first scale load.
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(grid);
+      cfg.blockDim = dim3(kGemmThreads);
+      cfg.dynamicSmemBytes = static_cast<size_t>(smem);
+      cfg.stream = stream;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = g_profile ? 0 : 1;  // timing events sit between the two launches
+      if (kind == kKindMxf8) {
+        CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<kKindMxf8>, tmA, tmB, tmC, p));
+      } else {
+        CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<kKindMxf4>, tmA, tmB, tmC, p));
+      }
     }
     g_launches.fetch_add(1);
     CUDA_TRY(cudaGetLastError());
@@ -1010,7 +998,6 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
     set_error("device-side bounded wait timed out (code %d)", *st.error_host);
     *st.error_host = 0;
     cudaMemsetAsync(st.error_dev, 0, sizeof(int32_t), stream);
-    cudaMemsetAsync(st.decode_counters, 0, kDecodeCounterSlots * sizeof(int32_t), stream);
     cudaStreamSynchronize(stream);
     return CPUOPS_B200_STATUS_DEVICE_TIMEOUT;
   }

@@ -32,60 +32,82 @@ struct ScaleLayout {
   int tiles, stages;       // number of row tiles, pipeline stages along k
 };
 
-__device__ __forceinline__ void relayout_one_atom(const uint8_t* __restrict__ src,
-                                                  uint8_t* __restrict__ dst, const ScaleLayout& L,
-                                                  int64_t w, int lane) {
-  const bool vec_ok = (L.ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(src) & 3u) == 0);
+// One warp re-lays-out four consecutive atoms along k of one 128-row group: lane l
+// reads 16 scale bytes (four 4-block quads) of rows l, 32 + l, 64 + l and 96 + l and
+// writes one 16-byte piece (its row of each of the four 32-row sub-groups) per atom,
+// so every atom is written as one coalesced 512-byte line.  Rows, k blocks and tile
+// rows outside the matrix read as 0x7F (scale 1.0; the operand data there is zero).
+__device__ __forceinline__ void relayout_four_atoms(const uint8_t* __restrict__ src,
+                                                    uint8_t* __restrict__ dst, const ScaleLayout& L,
+                                                    int64_t w, int lane) {
   const int k_atoms = L.stages * L.ka;
-  const int kq = static_cast<int>(w % k_atoms);  // atom index along k
-  const int64_t rg = w / k_atoms;                // (tile, nb)
+  const int k_groups = (k_atoms + 3) >> 2;
+  const int kg = static_cast<int>(w % k_groups);
+  const int64_t rg = w / k_groups;  // (tile, nb)
   const int nb = static_cast<int>(rg % L.nb128);
   const int tile = static_cast<int>(rg / L.nb128);
-  const int stage = kq / L.ka, ka = kq % L.ka;
-  const int kb0 = stage * L.bps + ka * 4;
-  uint32_t words[4];
+  const int kb0 = kg * 16;
+  const bool vec_ok = (L.ld % 16 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) &&
+                      kb0 + 15 < L.kblocks;
+  uint32_t words[4][4];  // [sub-group][atom]
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
     const int r_in_tile = nb * 128 + g * 32 + lane;
     const int row = tile * L.tile_rows + r_in_tile;
-    uint32_t word = 0x7F7F7F7Fu;
-    if (r_in_tile < L.tile_rows && row < L.rows && kb0 < L.kblocks) {
-      const uint8_t* s = src + static_cast<int64_t>(row) * L.ld + kb0;
-      if (vec_ok && kb0 + 3 < L.kblocks) {
-        word = *reinterpret_cast<const uint32_t*>(s);
-      } else {
-        word = 0;
+    const bool row_ok = r_in_tile < L.tile_rows && row < L.rows;
+    const uint8_t* s = src + static_cast<int64_t>(row) * L.ld + kb0;
+    if (row_ok && vec_ok) {
+      const uint4 v = *reinterpret_cast<const uint4*>(s);
+      words[g][0] = v.x; words[g][1] = v.y; words[g][2] = v.z; words[g][3] = v.w;
+    } else {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint32_t b = (kb0 + j < L.kblocks) ? s[j] : 127u;
-          word |= b << (8 * j);
+      for (int j = 0; j < 4; ++j) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const int kb = kb0 + 4 * j + t;
+          const uint32_t byte = (row_ok && kb < L.kblocks) ? s[4 * j + t] : 127u;
+          word |= byte << (8 * t);
         }
+        words[g][j] = word;
       }
     }
-    words[g] = word;
   }
-  const int64_t atom_off =
-      ((static_cast<int64_t>(tile) * L.stages + stage) * (L.ka * L.nb128) + ka * L.nb128 + nb) * 512;
-  *reinterpret_cast<uint4*>(dst + atom_off + lane * 16) =
-      make_uint4(words[0], words[1], words[2], words[3]);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int kq = kg * 4 + j;
+    if (kq < k_atoms) {
+      const int stage = kq / L.ka, ka = kq % L.ka;
+      const int64_t atom_off =
+          ((static_cast<int64_t>(tile) * L.stages + stage) * (L.ka * L.nb128) + ka * L.nb128 + nb) * 512;
+      *reinterpret_cast<uint4*>(dst + atom_off + lane * 16) =
+          make_uint4(words[0][j], words[1][j], words[2][j], words[3][j]);
+    }
+  }
+}
+
+__host__ __device__ inline int64_t relayout_work_items(const ScaleLayout& L) {
+  return static_cast<int64_t>(L.tiles) * L.nb128 * ((L.stages * L.ka + 3) / 4);
 }
 
 // One launch re-lays-out up to two scale arrays (the A-side and B-side operands
-// of one GEMM).  Work order: consecutive warps walk k for a fixed 128-row group,
-// so the 32-byte sectors of the source rows are reused out of L1/L2.
+// of one GEMM).  The GEMM kernel that consumes the result may be launched with
+// programmatic stream serialization: its prologue then overlaps this kernel, and
+// its TMA producer waits (griddepcontrol.wait) before the first scale load.
 __global__ void relayout_scales_kernel(const uint8_t* __restrict__ src0, uint8_t* __restrict__ dst0,
                                        ScaleLayout L0, const uint8_t* __restrict__ src1,
                                        uint8_t* __restrict__ dst1, ScaleLayout L1) {
-  const int64_t atoms0 = static_cast<int64_t>(L0.tiles) * L0.stages * L0.ka * L0.nb128;
-  const int64_t atoms1 = src1 ? static_cast<int64_t>(L1.tiles) * L1.stages * L1.ka * L1.nb128 : 0;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int64_t items0 = relayout_work_items(L0);
+  const int64_t items1 = src1 ? relayout_work_items(L1) : 0;
   const int lane = threadIdx.x & 31;
   const int64_t warp0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-  for (int64_t w = warp0; w < atoms0 + atoms1; w += nwarps) {
-    if (w < atoms0) {
-      relayout_one_atom(src0, dst0, L0, w, lane);
+  for (int64_t w = warp0; w < items0 + items1; w += nwarps) {
+    if (w < items0) {
+      relayout_four_atoms(src0, dst0, L0, w, lane);
     } else {
-      relayout_one_atom(src1, dst1, L1, w - atoms0, lane);
+      relayout_four_atoms(src1, dst1, L1, w - items0, lane);
     }
   }
 }

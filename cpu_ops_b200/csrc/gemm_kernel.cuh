@@ -29,7 +29,7 @@
 
 namespace b200 {
 
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 224;  // producer, MMA issuer, 4 epilogue warps, scale copier
 constexpr uint32_t kTmemCols = 512;
 constexpr int kRasterGroupM = 8;
 
@@ -166,6 +166,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * kMaxStages + 2 + b); };
   const uint32_t drain_bar = bar_base + 8u * (2 * kMaxStages + 4);
   auto c_full_bar = [&](int w, int b) { return bar_base + 8u * (2 * kMaxStages + 5 + w * 2 + b); };
+  auto sf_full_bar = [&](uint32_t q) { return bar_base + 8u * (40u + q); };  // 8 slots
+  const uint32_t sf_drain_bar = bar_base + 8u * 48u;
   uint32_t* tmem_slot =
       reinterpret_cast<uint32_t*>(smem + (bar_base - smem_base) + 8 * (2 * kMaxStages + 5 + 8));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -180,6 +182,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       mbar_init(acc_empty_bar(b), 4);  // one arrival per epilogue warp
     }
     mbar_init(drain_bar, 1);
+    mbar_init(sf_drain_bar, 1);
+    for (uint32_t q = 0; q < 8; ++q) mbar_init(sf_full_bar(q), 1);  // tcgen05.commit of the scale copies
     for (int w = 0; w < 4; ++w)
       for (int b = 0; b < 2; ++b) mbar_init(c_full_bar(w, b), 1);  // TMA load of one C chunk
     *abort_flag = 0;
@@ -200,8 +204,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
   const int total_tiles = p.m_tiles * p.n_tiles * p.slices;
   const int nacc = p.nacc;
+  // MX: the tensor-memory columns left over after the accumulators hold a ring of
+  // scale-factor slots (one k-block each: the A atoms, then the B atoms, 4 columns per
+  // atom).  A dedicated thread fills them; copies issued by the MMA thread itself
+  // execute in line with its MMAs and cost the tensor pipe ~90 cycles each.
+  const uint32_t sfa_atoms = p.sfa_stage_bytes / 512, sfb_atoms = p.sfb_stage_bytes / 512;
+  const uint32_t sf_atoms = sfa_atoms + sfb_atoms;
+  const uint32_t sf_cols = 4u * sf_atoms;
+  const uint32_t sf_col0 = static_cast<uint32_t>(nacc * p.BN);
+  uint32_t sf_slots = 1;
+  if constexpr (kMx) sf_slots = min(8u, max(1u, (kTmemCols - sf_col0) / max(sf_cols, 1u)));
+  const uint64_t sf_hi64 = make_smem_desc_hi(0, 128, 0);  // 32 rows x 16 B, 8-row groups 128 B apart
   long long dbg_c0 = 0;
   uint64_t dbg_t0 = 0;
+  if (p.clk_dbg != nullptr && threadIdx.x == 0) atomicMin(p.clk_dbg + 8, global_timer_ns());
   if (p.clk_dbg != nullptr && blockIdx.x == 0 && threadIdx.x == 64) {
     dbg_c0 = clock64();
     dbg_t0 = global_timer_ns();
@@ -218,6 +234,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       uint32_t full_addr = full0, empty_addr = empty0, a_dst = smem_base, sf_dst = sf_base;
       const int a_mn = p.a_mn_major, b_mn = p.b_mn_major, b_chunks = p.BN / 128;
       const uint32_t sfa_bytes = p.sfa_stage_bytes, sfb_bytes = p.sfb_stage_bytes;
+      // The scale atoms come from the re-layout kernel launched just before this one,
+      // which may still be running (programmatic stream serialization).
+      if constexpr (kMx) asm volatile("griddepcontrol.wait;" ::: "memory");
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const TileCoord tc = decode_tile(p, t);
         const int m0 = tc.m_tile * kTileM, n0 = tc.n_tile * p.BN;
@@ -291,9 +310,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       // second 128-column chunk of B starts 128 rows (16384 bytes) later.
       const uint64_t a_hi64 = p.a_mn_major ? make_smem_desc_hi(16384, 1024, 2) : make_smem_desc_hi(16, 1024, 2);
       const uint64_t b_hi64 = p.b_mn_major ? make_smem_desc_hi(16384, 1024, 2) : make_smem_desc_hi(16, 1024, 2);
-      const uint64_t sf_hi64 = make_smem_desc_hi(0, 128, 0);  // 32 rows x 16 B, 8-row groups 128 B apart
       const uint32_t a_hi = static_cast<uint32_t>(a_hi64 >> 32), b_hi = static_cast<uint32_t>(b_hi64 >> 32);
-      const uint32_t sf_hi = static_cast<uint32_t>(sf_hi64 >> 32);
       const uint32_t a_lo0 = static_cast<uint32_t>(a_hi64) | (smem_base >> 4);
       const uint32_t b_lo0 = static_cast<uint32_t>(b_hi64) | ((smem_base + kTileM * 128) >> 4);
       const uint32_t stage_step = static_cast<uint32_t>(stage_bytes) >> 4;
@@ -309,23 +326,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         id1 = idesc_with_sf_ids(idesc, 2, 2);
         id3 = id1;
       }
-      const uint32_t sf_col0 = static_cast<uint32_t>(nacc * p.BN);
-      const uint32_t sfa_atoms = p.sfa_stage_bytes / 512, sfb_atoms = p.sfb_stage_bytes / 512;
-      const uint32_t sf_atoms = sfa_atoms + sfb_atoms;
-      // TMEM scale columns: the k-block's A atoms, then its B atoms (4 columns each)
-      const uint32_t sfa_t = tmem_base + sf_col0;
-      const uint32_t sfb_t = sfa_t + 4u * sfa_atoms;
+      const uint32_t sf_t0 = tmem_base + sf_col0;
+      uint32_t sfa_t = sf_t0, sf_q = 0, sf_ph = 0, peek_sf = 0;
       const uint32_t sfa_half = 4u, sfb_half = 2u * sfb_atoms;  // mxf4: second 4-block atom row
-      const uint32_t sf_step = static_cast<uint32_t>(sf_stage) >> 4;
-      const uint32_t sf_lo0 = static_cast<uint32_t>(sf_hi64) | (sf_base >> 4);
       const uint32_t full0 = full_bar(0), empty0 = empty_bar(0);
 
       const bool dbg = p.clk_dbg != nullptr && blockIdx.x == 0;
-      long long dbg_wait_acc = 0, dbg_wait_full = 0;
+      long long dbg_wait_acc = 0, dbg_wait_full = 0, dbg_wait_sf = 0;
       const long long dbg_start = dbg ? clock64() : 0;
       int s = 0, buf = 0;
-      uint32_t ph = 0, acc_ph = 0;
-      uint32_t a_lo = a_lo0, b_lo = b_lo0, full_addr = full0, empty_addr = empty0, sf_lo = sf_lo0;
+      uint32_t ph = 0, acc_ph = 0, peek = 0;
+      uint32_t a_lo = a_lo0, b_lo = b_lo0, full_addr = full0, empty_addr = empty0;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const TileCoord tc = decode_tile(p, t);
         long long tw0 = dbg ? clock64() : 0;
@@ -339,21 +350,31 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         uint32_t accumulate = 0;
         for (int i = 0; i < tc.nkb; ++i) {
           tw0 = dbg ? clock64() : 0;
-          if (!mbar_wait_bounded(full_addr, ph, abort_flag)) {
+          if (!peek && !mbar_wait_bounded(full_addr, ph, abort_flag)) {
             record_error(p, abort_flag, kErrMmaWaitFull);
             ok = false;
             break;
           }
           if (dbg) dbg_wait_full += clock64() - tw0;
-          tc_fence_after_sync();
+          // probe the next ring slot now; the answer is consumed after this k-block's
+          // MMAs have been issued
+          const uint32_t nfull = (s + 1 == stages) ? full0 : full_addr + 8;
+          const uint32_t nph = (s + 1 == stages) ? (ph ^ 1u) : ph;
+          peek = mbar_test_wait(nfull, nph);
+          const uint32_t sfb_t = sfa_t + 4u * sfa_atoms;
           if constexpr (kMx) {
-            // The k-block's scale factors: shared -> tensor memory.  Issued by the same
-            // thread ahead of the MMAs that read them, so the pipe orders them; the
-            // copies run while earlier MMAs are still executing.
-            uint32_t src = sf_lo, dst = sfa_t;
-            for (uint32_t a = 0; a < sf_atoms; ++a, src += 32, dst += 4)
-              tmem_cp_32x128b_warpx4_w(dst, src, sf_hi);
+            // the k-block's scale factors, copied into this slot by the scale copier
+            tw0 = dbg ? clock64() : 0;
+            if (!peek_sf && !mbar_wait_bounded(sf_full_bar(sf_q), sf_ph, abort_flag)) {
+              record_error(p, abort_flag, kErrMmaWaitFull);
+              ok = false;
+              break;
+            }
+            if (dbg) dbg_wait_sf += clock64() - tw0;
+            const bool wrap = sf_q + 1 == sf_slots;
+            peek_sf = mbar_test_wait(sf_full_bar(wrap ? 0u : sf_q + 1), wrap ? (sf_ph ^ 1u) : sf_ph);
           }
+          tc_fence_after_sync();
           if constexpr (KIND == kKindI8) {
             mma_i8_w(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc, accumulate);
             mma_i8_w(d_tmem, a_lo + a_k, a_hi, b_lo + b_k, b_hi, idesc, 1u);
@@ -372,6 +393,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
           accumulate = 1u;
           tc_commit(empty_addr);  // frees the stage once these MMAs (and copies) have read it
+          if constexpr (kMx) {
+            sfa_t += sf_cols;
+            if (++sf_q == sf_slots) {
+              sf_q = 0;
+              sf_ph ^= 1u;
+              sfa_t = sf_t0;
+            }
+          }
           if (++s == stages) {
             s = 0;
             ph ^= 1u;
@@ -379,13 +408,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             b_lo = b_lo0;
             full_addr = full0;
             empty_addr = empty0;
-            sf_lo = sf_lo0;
           } else {
             a_lo += stage_step;
             b_lo += stage_step;
             full_addr += 8;
             empty_addr += 8;
-            sf_lo += sf_step;
           }
         }
         if (ok) tc_commit(acc_full_bar(buf));
@@ -402,6 +429,76 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         p.clk_dbg[2] = static_cast<unsigned long long>(clock64() - dbg_start);
         p.clk_dbg[3] = static_cast<unsigned long long>(dbg_wait_full);
         p.clk_dbg[4] = static_cast<unsigned long long>(dbg_wait_acc);
+        p.clk_dbg[7] = static_cast<unsigned long long>(dbg_wait_sf);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 6) {
+    // ------------------------------ scale copier ------------------------------
+    // MX only.  For every k-block: wait for its stage to land, wait until the MMAs that
+    // last read the target slot are done, copy the atoms shared -> tensor memory and let
+    // tcgen05.commit announce them on the slot's barrier.
+    if constexpr (kMx) {
+      if (lane == 0) {
+        const uint32_t sf_hi = static_cast<uint32_t>(sf_hi64 >> 32);
+        const uint32_t sf_lo0 = static_cast<uint32_t>(sf_hi64) | (sf_base >> 4);
+        const uint32_t sf_step = static_cast<uint32_t>(sf_stage) >> 4;
+        const uint32_t sf_t0 = tmem_base + sf_col0;
+        // With fewer slots than stages the slot's previous readers are the MMAs of the
+        // k-block `sf_slots` earlier: their commit is the empty barrier of that stage.
+        // With at least as many slots as stages the stage's own full barrier implies it.
+        const bool need_free = sf_slots < static_cast<uint32_t>(stages);
+        int s = 0, fs = 0;            // stage of this k-block / of the k-block sf_slots earlier
+        uint32_t ph = 0, fph = 0, q = 0, it = 0, peek_full = 0;
+        uint32_t sf_lo = sf_lo0, dst0 = sf_t0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+          const TileCoord tc = decode_tile(p, t);
+          for (int i = 0; i < tc.nkb; ++i, ++it) {
+            if (!peek_full && !mbar_wait_bounded(full_bar(s), ph, abort_flag)) {
+              record_error(p, abort_flag, kErrMmaWaitFull);
+              ok = false;
+              break;
+            }
+            if (need_free && it >= sf_slots) {
+              if (!mbar_wait_bounded(empty_bar(fs), fph, abort_flag)) {
+                record_error(p, abort_flag, kErrMmaWaitFull);
+                ok = false;
+                break;
+              }
+              if (++fs == stages) {
+                fs = 0;
+                fph ^= 1u;
+              }
+            }
+            {
+              const int ns = (s + 1 == stages) ? 0 : s + 1;
+              peek_full = mbar_test_wait(full_bar(ns), ns == 0 ? (ph ^ 1u) : ph);
+            }
+            tc_fence_after_sync();
+            uint32_t src = sf_lo, dst = dst0;
+            for (uint32_t a = 0; a < sf_atoms; ++a, src += 32, dst += 4)
+              tmem_cp_32x128b_warpx4_w(dst, src, sf_hi);
+            tc_commit(sf_full_bar(q));
+            if (++q == sf_slots) {
+              q = 0;
+              dst0 = sf_t0;
+            } else {
+              dst0 += sf_cols;
+            }
+            if (++s == stages) {
+              s = 0;
+              ph ^= 1u;
+              sf_lo = sf_lo0;
+            } else {
+              sf_lo += sf_step;
+            }
+          }
+        }
+        // no copy may be in flight when tensor memory is released
+        tc_commit(sf_drain_bar);
+        int dummy = 0;
+        if (!mbar_wait_bounded(sf_drain_bar, 0, &dummy)) record_error(p, abort_flag, kErrDrainWait);
       }
     }
     __syncwarp();
@@ -500,6 +597,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if (p.clk_dbg != nullptr && threadIdx.x == 0) atomicMax(p.clk_dbg + 9, global_timer_ns());
 }
 
 }  // namespace b200

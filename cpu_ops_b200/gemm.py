@@ -225,8 +225,22 @@ class _Operator:
         self._memory_space = memory_space
         self._device = device
         self._tile_n = tile_n
+        self._gemm = _capi.load().cpuops_b200_gemm
 
-    def _finish(self, desc: _capi.GemmDesc, args) -> Status:
+    def run(self, desc: _capi.GemmDesc) -> Status:
+        """Issues one call with a descriptor built earlier by ``describe``.
+
+        A C++ caller of the reference builds ``Arguments`` on the stack for free; a
+        Python loop that issues the same GEMM repeatedly (a decode loop) can keep the
+        descriptor instead of paying for its construction on every call.
+        """
+        return Status(self._gemm(C.byref(desc)))
+
+    def __call__(self, args, num_threads: int = 0) -> Status:
+        del num_threads  # accepted for source compatibility; the GPU grid replaces the pool
+        return self.run(self.describe(args))
+
+    def _finish(self, desc: _capi.GemmDesc, args) -> _capi.GemmDesc:
         desc.struct_size = C.sizeof(_capi.GemmDesc)
         desc.split_k_slices = int(args.split_k_slices)
         desc.memory_space = self._memory_space
@@ -234,7 +248,7 @@ class _Operator:
         desc.flags = _capi.FLAG_ASYNC if self._async else 0
         desc.device = self._device
         desc.tile_n = self._tile_n
-        return Status(_capi.load().cpuops_b200_gemm(C.byref(desc)))
+        return desc
 
 
 class GemmU8S8S32(_Operator):
@@ -247,8 +261,8 @@ class GemmU8S8S32(_Operator):
         super().__init__(**kw)
         self.LayoutA, self.LayoutB, self.LayoutC = layout_a, layout_b, layout_c
 
-    def __call__(self, args: GemmArguments, num_threads: int = 0) -> Status:
-        del num_threads  # accepted for source compatibility; the GPU grid replaces the pool
+    def describe(self, args: GemmArguments) -> _capi.GemmDesc:
+        """The C-ABI descriptor of one call (pointers are read now, not at run time)."""
         desc = _capi.GemmDesc()
         desc.kind = _capi.KIND_I8
         desc.a_format, desc.b_format = _capi.FMT_U8, _capi.FMT_S8
@@ -304,8 +318,8 @@ class GemmMx(_Operator):
         self.StorageB = storage_b or storage_a
         self.LayoutC = layout_c
 
-    def __call__(self, args: GemmMxArguments, num_threads: int = 0) -> Status:
-        del num_threads
+    def describe(self, args: GemmMxArguments) -> _capi.GemmDesc:
+        """The C-ABI descriptor of one call (pointers are read now, not at run time)."""
         desc = _capi.GemmDesc()
         desc.kind = _capi.KIND_MX
         desc.a_format, desc.b_format = self.StorageA.fmt, self.StorageB.fmt
