@@ -71,6 +71,12 @@ struct DeviceState {
     size_t bytes = 0;
   };
   std::map<cudaStream_t, Workspace> ws;
+  // Host-operand calls are cut into row panels that run on these streams, so that one
+  // panel's upload, another's GEMM and a third's download overlap (see gemm_body).
+  static constexpr int kPanelStreams = 3;
+  cudaStream_t panel_stream[kPanelStreams] = {nullptr, nullptr, nullptr};
+  cudaEvent_t panel_done[kPanelStreams] = {nullptr, nullptr, nullptr};
+  cudaEvent_t fork_event = nullptr;
 };
 
 // Optional timing of the tensor-core kernel alone (events on the launching stream).
@@ -126,6 +132,11 @@ int init_device(int device, DeviceState** out) {
     CUDA_TRY(cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, device));
     CUDA_TRY(cudaDeviceGetAttribute(&st.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
     CUDA_TRY(cudaStreamCreateWithFlags(&st.stream, cudaStreamNonBlocking));
+    for (int j = 0; j < DeviceState::kPanelStreams; ++j) {
+      CUDA_TRY(cudaStreamCreateWithFlags(&st.panel_stream[j], cudaStreamNonBlocking));
+      CUDA_TRY(cudaEventCreateWithFlags(&st.panel_done[j], cudaEventDisableTiming));
+    }
+    CUDA_TRY(cudaEventCreateWithFlags(&st.fork_event, cudaEventDisableTiming));
     CUDA_TRY(cudaMalloc(&st.error_dev, sizeof(int32_t)));
     CUDA_TRY(cudaMemset(st.error_dev, 0, sizeof(int32_t)));
     CUDA_TRY(cudaMallocHost(&st.error_host, sizeof(int32_t)));
@@ -480,7 +491,23 @@ CPUOPS_B200_API int cpuops_b200_profile_collect(double* total_ms, int32_t* launc
   return 0;
 }
 
+}  // extern "C"
+
+// The whole call.  depth 0: a caller's descriptor.  depth 1: one row panel of a
+// host-operand call, issued by depth 0 on one of the panel streams (asynchronous, with
+// host pointers allowed: the parent synchronises).  g_mu is held by the caller.
+static int gemm_body(const cpuops_b200_gemm_desc* d, int depth);
+
+extern "C" {
+
 CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  return gemm_body(d, 0);
+}
+
+}  // extern "C"
+
+static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
   if (!d || d->struct_size != sizeof(cpuops_b200_gemm_desc)) {
     set_error("descriptor is null or struct_size does not match this library (ABI %d)",
               CPUOPS_B200_ABI_VERSION);
@@ -550,7 +577,6 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
       return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
   }
 
-  std::lock_guard<std::mutex> lk(g_mu);
   DeviceState* stp = nullptr;
   if (int rc = init_device(d->device, &stp)) return rc;
   DeviceState& st = *stp;
@@ -570,7 +596,7 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
     op_dev[t] = !d->ops[t].ptr || is_device_pointer(d->ops[t].ptr, d->memory_space);
   const bool any_host = !(a_dev && b_dev && sa_dev && sb_dev && c_dev && d_dev) ||
                         std::any_of(op_dev, op_dev + d->n_ops, [](bool x) { return !x; });
-  if (async && any_host) {
+  if (async && any_host && depth == 0) {
     set_error("FLAG_ASYNC needs every operand in device memory");
     return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
   }
@@ -642,6 +668,85 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
         }
       }
     }
+  }
+
+  // ---- host operands of a large problem: row panels on three streams ---------------------
+  // A call whose A and D live in host memory is bound by the PCIe copies, not by the
+  // GEMM.  Run serially (upload everything, compute, download everything) the two copy
+  // directions never overlap.  Instead: stage the B side once, then cut the output rows
+  // into panels and issue each panel as its own call (host A/C/D rows, device B) on one
+  // of three streams; a panel's upload, its neighbour's GEMM and the download of the
+  // one before overlap, and both copy engines stay busy.  Every panel uses the tile
+  // width and the single k slice chosen for the whole problem, so each element is
+  // computed exactly as the unsplit call would compute it.
+  if (depth == 0 && k > 0 && !a_dev && !d_dev && !ch.swap && ch.slices == 1 && m >= 1024) {
+    Plan bplan;
+    size_t pb = 0, psb = 0;
+    const int64_t b_pitch_staged = align_up(B.inner_bytes, 16);
+    if (!b_dev) pb = bplan.take(b_pitch_staged * B.outer);
+    if (is_mx && !sb_dev) psb = bplan.take(static_cast<size_t>(n) * d->ld_scales_b);
+    uint8_t* bw = nullptr;
+    if (bplan.total > 0) {
+      if (int rc = ensure_workspace(st, stream, bplan.total, &bw)) return rc;
+    }
+    cpuops_b200_gemm_desc sub = *d;
+    if (!b_dev) {
+      CUDA_TRY(cudaMemcpy2DAsync(bw + pb, b_pitch_staged, d->b, B.pitch, B.inner_bytes, B.outer,
+                                 cudaMemcpyHostToDevice, stream));
+      sub.b = bw + pb;
+      sub.ldb = static_cast<int32_t>(fp4_b ? b_pitch_staged * 2 : b_pitch_staged);
+    }
+    if (is_mx && !sb_dev) {
+      CUDA_TRY(cudaMemcpyAsync(bw + psb, d->b_scales,
+                               static_cast<size_t>(n - 1) * d->ld_scales_b + (k + 31) / 32,
+                               cudaMemcpyHostToDevice, stream));
+      sub.b_scales = bw + psb;
+    }
+    CUDA_TRY(cudaEventRecord(st.fork_event, stream));
+    sub.memory_space = CPUOPS_B200_MEM_AUTO;
+    sub.flags |= CPUOPS_B200_FLAG_ASYNC;
+    sub.split_k_slices = 1;
+    sub.tile_n = ch.BN;
+    const int n_panels = std::max(2, std::min(8, m / 512));
+    const int panel_rows = static_cast<int>(align_up((m + n_panels - 1) / n_panels, 128));
+    int issued = 0;
+    for (int row0 = 0; row0 < m; row0 += panel_rows, ++issued) {
+      const int j = issued % DeviceState::kPanelStreams;
+      if (issued < DeviceState::kPanelStreams)
+        CUDA_TRY(cudaStreamWaitEvent(st.panel_stream[j], st.fork_event, 0));
+      cpuops_b200_gemm_desc pd = sub;
+      pd.m = std::min(panel_rows, m - row0);
+      pd.stream = st.panel_stream[j];
+      // A: k-major rows of m (row pitch A.pitch bytes), or m contiguous (int8 column-major)
+      pd.a = static_cast<const uint8_t*>(d->a) + (a_kmajor ? row0 * A.pitch : static_cast<int64_t>(row0));
+      if (is_mx)
+        pd.a_scales = static_cast<const uint8_t*>(d->a_scales) + static_cast<int64_t>(row0) * d->ld_scales_a;
+      const int64_t c_off = c_rm ? static_cast<int64_t>(row0) * d->ldc : row0;
+      const int64_t d_off = c_rm ? static_cast<int64_t>(row0) * d->ldd : row0;
+      pd.c = static_cast<const uint8_t*>(d->c) + c_off * 4;
+      pd.d = static_cast<uint8_t*>(d->d) + d_off * 4;
+      for (int t = 0; t < pd.n_ops; ++t)
+        if (pd.ops[t].opcode == CPUOPS_B200_OP_SCALE_PER_ROW)
+          pd.ops[t].ptr = static_cast<const uint8_t*>(d->ops[t].ptr) + static_cast<int64_t>(row0) * 4;
+      if (int rc = gemm_body(&pd, 1)) {
+        for (int q = 0; q < DeviceState::kPanelStreams; ++q) cudaStreamSynchronize(st.panel_stream[q]);
+        return rc;
+      }
+    }
+    for (int j = 0; j < std::min(issued, static_cast<int>(DeviceState::kPanelStreams)); ++j) {
+      CUDA_TRY(cudaEventRecord(st.panel_done[j], st.panel_stream[j]));
+      CUDA_TRY(cudaStreamWaitEvent(stream, st.panel_done[j], 0));
+    }
+    CUDA_TRY(cudaMemcpyAsync(st.error_host, st.error_dev, sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+    CUDA_TRY(cudaStreamSynchronize(stream));
+    if (*st.error_host != 0) {
+      set_error("device-side bounded wait timed out (code %d)", *st.error_host);
+      *st.error_host = 0;
+      cudaMemsetAsync(st.error_dev, 0, sizeof(int32_t), stream);
+      cudaStreamSynchronize(stream);
+      return CPUOPS_B200_STATUS_DEVICE_TIMEOUT;
+    }
+    return CPUOPS_B200_STATUS_SUCCESS;
   }
 
   // ---- workspace plan ------------------------------------------------------------------
@@ -1003,9 +1108,6 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
   }
   return CPUOPS_B200_STATUS_SUCCESS;
 }
-
-
-}  // extern "C"
 
 // =================================================================================
 // Allocation-free split-k entry point
