@@ -29,6 +29,7 @@ ACT_NONE, ACT_RELU = 0, 1
 OP_RELU, OP_CLAMP, OP_BIAS_ADD, OP_SCALE_PER_ROW, OP_SCALE_PER_COL, OP_GELU, OP_SILU = range(1, 8)
 MEM_AUTO, MEM_HOST, MEM_DEVICE = 0, 1, 2
 FLAG_ASYNC = 1
+FLAG_PAIR_ON, FLAG_PAIR_OFF = 2, 4
 NOALLOC_SCRATCH_BYTES = 8 << 20
 
 # Every symbol include/cpu_ops_b200.h declares.
@@ -42,10 +43,18 @@ EXPORTED_SYMBOLS = (
     "cpuops_b200_profile",
     "cpuops_b200_profile_collect",
     "cpuops_b200_launch_count",
+    "cpuops_b200_last_plan",
     "cpuops_b200_last_error",
     "cpuops_b200_abi_version",
     "cpuops_b200_device_count",
 )
+
+
+class Plan(C.Structure):
+    """cpuops_b200_plan: what the last GEMM call launched (diagnostics)."""
+    _fields_ = [("swapped", C.c_int32), ("tile_n", C.c_int32), ("pair", C.c_int32),
+                ("slices", C.c_int32), ("stages", C.c_int32), ("grid", C.c_int32),
+                ("c_ring", C.c_int32), ("reserved", C.c_int32)]
 
 
 class Scalar(C.Union):
@@ -104,11 +113,19 @@ def load() -> C.CDLL:
     lib.cpuops_b200_profile_collect.restype = C.c_int
     lib.cpuops_b200_profile_collect.argtypes = [C.POINTER(C.c_double), C.POINTER(C.c_int32)]
     lib.cpuops_b200_launch_count.restype = C.c_uint64
+    lib.cpuops_b200_last_plan.restype = C.c_int
+    lib.cpuops_b200_last_plan.argtypes = [C.POINTER(Plan)]
     lib.cpuops_b200_last_error.restype = C.c_char_p
     lib.cpuops_b200_abi_version.restype = C.c_int
     lib.cpuops_b200_device_count.restype = C.c_int
     _lib = lib
     return lib
+
+
+def last_plan() -> Plan:
+    plan = Plan()
+    load().cpuops_b200_last_plan(C.byref(plan))
+    return plan
 
 
 def last_error() -> str:

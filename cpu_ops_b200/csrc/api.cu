@@ -77,6 +77,9 @@ struct DeviceState {
   cudaStream_t panel_stream[kPanelStreams] = {nullptr, nullptr, nullptr};
   cudaEvent_t panel_done[kPanelStreams] = {nullptr, nullptr, nullptr};
   cudaEvent_t fork_event = nullptr;
+  // Largest number of two-CTA clusters of the pair kernel that can be resident at once,
+  // per kind (-1: not asked yet; 0: cluster launch unavailable).
+  int pair_clusters[3] = {-1, -1, -1};
 };
 
 // Optional timing of the tensor-core kernel alone (events on the launching stream).
@@ -84,6 +87,8 @@ bool g_profile = false;
 std::vector<std::pair<cudaEvent_t, cudaEvent_t>> g_profile_events;
 
 unsigned long long* g_clk_buf = nullptr;  // experiments only (CPUOPS_B200_CLK)
+
+cpuops_b200_plan g_last_plan = {};
 
 std::mutex g_mu;  // serialises calls (the CPU library serialises on its pool mutex too)
 DeviceState g_dev[64];
@@ -151,11 +156,17 @@ int init_device(int device, DeviceState** out) {
       }
       g_encode = reinterpret_cast<EncodeTiledFn>(fn);
     }
-    CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindI8>,
+    CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindI8, false>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
-    CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindMxf8>,
+    CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindMxf8, false>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
-    CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindMxf4>,
+    CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindMxf4, false>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
+    CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindI8, true>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
+    CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindMxf8, true>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
+    CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindMxf4, true>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
     st.ready = true;
   } else {
@@ -189,6 +200,8 @@ struct EnvSwitches {
   bool no_c_ring = getenv("CPUOPS_B200_NO_C_RING") != nullptr;
   bool clk = getenv("CPUOPS_B200_CLK") != nullptr;
   int debug_flags = getenv("CPUOPS_B200_DEBUG") ? atoi(getenv("CPUOPS_B200_DEBUG")) : 0;
+  int raster_m = getenv("CPUOPS_B200_RASTER") ? atoi(getenv("CPUOPS_B200_RASTER")) : 0;
+  int pair = getenv("CPUOPS_B200_PAIR") ? atoi(getenv("CPUOPS_B200_PAIR")) : -1;  // -1: heuristic
 };
 const EnvSwitches& env_switches() {
   static const EnvSwitches e;
@@ -283,6 +296,33 @@ int make_tensor_map_words(CUtensorMap* tm, const void* base, uint64_t cols, uint
   return 0;
 }
 
+// The re-laid-out scale array as rows of one 512-byte atom each (128 words, not
+// swizzled); a box is the `box_atoms` atoms of one k-block.
+int make_tensor_map_atoms(CUtensorMap* tm, const void* base, uint64_t n_atoms, uint32_t box_atoms) {
+  const TensorMapKey key{reinterpret_cast<uint64_t>(base), 128, n_atoms, 512, box_atoms, 2u};
+  TensorMapSlot& slot = tensor_map_slot(key);
+  if (slot.valid && slot.key == key) {
+    *tm = slot.map;
+    return 0;
+  }
+  const cuuint64_t dims[2] = {128, n_atoms};
+  const cuuint64_t strides[1] = {512};
+  const cuuint32_t box[2] = {128, box_atoms};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r =
+      g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box,
+               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled (scale atoms) failed with %d", static_cast<int>(r));
+    return CPUOPS_B200_STATUS_CUDA_ERROR;
+  }
+  slot.valid = true;
+  slot.key = key;
+  slot.map = *tm;
+  return 0;
+}
+
 bool tma_addressable(const void* base, int64_t pitch_bytes, int64_t outer) {
   if (reinterpret_cast<uintptr_t>(base) & 15u) return false;
   if (outer > 1 && (pitch_bytes & 15)) return false;
@@ -322,6 +362,7 @@ struct Plan {
 
 struct Choice {
   bool swap = false;
+  bool pair = false;  // two-CTA clusters, 256-row tiles
   int BN = 128;
   int nacc = 2;
   int slices = 1;
@@ -360,6 +401,13 @@ CPUOPS_B200_API int cpuops_b200_abi_version(void) { return CPUOPS_B200_ABI_VERSI
 CPUOPS_B200_API const char* cpuops_b200_last_error(void) { return g_last_error; }
 
 CPUOPS_B200_API uint64_t cpuops_b200_launch_count(void) { return g_launches.load(); }
+
+CPUOPS_B200_API int cpuops_b200_last_plan(cpuops_b200_plan* out) {
+  if (!out) return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+  std::lock_guard<std::mutex> lk(g_mu);
+  *out = g_last_plan;
+  return 0;
+}
 
 CPUOPS_B200_API int cpuops_b200_device_count(void) {
   std::lock_guard<std::mutex> lk(g_mu);
@@ -670,6 +718,22 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     }
   }
 
+  // ---- one CTA per tile, or a pair of CTAs per 256-row tile ---------------------------------
+  // With one CTA per SM the k loop is bound by the L2 -> shared-memory feed: 48 KB per
+  // k-block for a 128 x 256 tile.  A pair of CTAs working on one 256-row tile stages only
+  // half of the B tile each (32 KB per k-block per SM for the same MMA work).
+  if (k > 0) {
+    const int Mk = ch.swap ? n : m, Nk = ch.swap ? m : n;
+    const bool bk_role_mn = !(ch.swap ? a_kmajor : b_kmajor);
+    const bool legal = Mk > 128 && (!bk_role_mn || ch.BN == 256) && ch.BN % 32 == 0;
+    const int64_t tiles = static_cast<int64_t>((Mk + 127) / 128) * ((Nk + ch.BN - 1) / ch.BN) * ch.slices;
+    bool want = tiles >= 2 * st.sm_count && k_blocks >= 8;
+    if (env_switches().pair >= 0) want = env_switches().pair != 0;
+    if (d->flags & CPUOPS_B200_FLAG_PAIR_ON) want = true;
+    if (d->flags & CPUOPS_B200_FLAG_PAIR_OFF) want = false;
+    ch.pair = legal && want;
+  }
+
   // ---- host operands of a large problem: row panels on three streams ---------------------
   // A call whose A and D live in host memory is bound by the PCIe copies, not by the
   // GEMM.  Run serially (upload everything, compute, download everything) the two copy
@@ -803,7 +867,9 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     Nk = ch.swap ? m : n;
     if (is_mx) {
       bps = fp4_a ? 8 : 4;
-      sfa_bytes = cpuops_b200_scale_layout_bytes(Mk, k, kTileM, bps);
+      // a pair always reads the scales of both of its 128-row halves
+      sfa_bytes = cpuops_b200_scale_layout_bytes(ch.pair ? static_cast<int>(align_up(Mk, 256)) : Mk, k,
+                                                 kTileM, bps);
       sfb_bytes = cpuops_b200_scale_layout_bytes(Nk, k, ch.BN, bps);
       off_sfa = plan.take(sfa_bytes);
       off_sfb = plan.take(sfb_bytes);
@@ -951,16 +1017,19 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
       const uint8_t* sbk = swap ? sa_ptr : sb_ptr;
       const int ldsak = swap ? d->ld_scales_b : d->ld_scales_a;
       const int ldsbk = swap ? d->ld_scales_a : d->ld_scales_b;
-      if (int rc = launch_relayout(sak, wsp + off_sfa, make_scale_layout(Mk, k, ldsak, kTileM, bps), sbk,
-                                   wsp + off_sfb, make_scale_layout(Nk, k, ldsbk, ch.BN, bps), stream))
+      ScaleLayout La = make_scale_layout(Mk, k, ldsak, kTileM, bps);
+      if (ch.pair) La.tiles = 2 * ((Mk + 255) / 256);  // rows past Mk read as scale 1.0
+      if (int rc = launch_relayout(sak, wsp + off_sfa, La, sbk, wsp + off_sfb,
+                                   make_scale_layout(Nk, k, ldsbk, ch.BN, bps), stream))
         return rc;
     }
 
     // ---- tensor maps -----------------------------------------------------------------------
     CUtensorMap tmA, tmB;
     if (int rc = make_tensor_map(&tmA, ak_ptr, AkM.inner_bytes, AkM.outer, ak_pitch, 128)) return rc;
+    const int b_rows = ch.pair ? ch.BN / 2 : ch.BN;  // rows of the B tile staged per CTA
     if (int rc = make_tensor_map(&tmB, bk_ptr, BkM.inner_bytes, BkM.outer, bk_pitch,
-                                 bk_kmajor ? static_cast<uint32_t>(ch.BN) : 128u))
+                                 bk_kmajor ? static_cast<uint32_t>(b_rows) : 128u))
       return rc;
 
     GemmParams p;
@@ -968,24 +1037,32 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     p.Mk = Mk;
     p.Nk = Nk;
     p.K = k;
-    p.m_tiles = (Mk + kTileM - 1) / kTileM;
+    const int tile_m = ch.pair ? 2 * kTileM : kTileM;
+    p.m_tiles = (Mk + tile_m - 1) / tile_m;
     p.n_tiles = (Nk + ch.BN - 1) / ch.BN;
     p.k_blocks = k_blocks;
     p.slices = ch.slices;
     p.BN = ch.BN;
     p.nacc = ch.nacc;
+    {
+      // One wave of CTAs covers g m-tiles x (SMs / g) n-tiles; its L2 footprint per
+      // k-block, g * 128 + (SMs / g) * BN rows, is smallest for g = sqrt(SMs * BN / 128).
+      int g = static_cast<int>(std::lround(std::sqrt(st.sm_count * ch.BN / 128.0))) / (ch.pair ? 2 : 1);
+      if (env_switches().raster_m > 0) g = env_switches().raster_m;
+      p.raster_m = std::max(1, std::min(g, p.m_tiles));
+    }
     p.a_mn_major = ak_kmajor ? 0 : 1;
     p.b_mn_major = bk_kmajor ? 0 : 1;
     if (!is_mx) {
       // A side is u8 unless the operands were swapped (then it is the caller's s8 B)
       const uint32_t a_fmt = swap ? 1u : 0u, b_fmt = swap ? 0u : 1u;
-      p.idesc = make_idesc(2 /*s32*/, a_fmt, b_fmt, p.a_mn_major, p.b_mn_major, kTileM, ch.BN);
+      p.idesc = make_idesc(2 /*s32*/, a_fmt, b_fmt, p.a_mn_major, p.b_mn_major, tile_m, ch.BN);
     } else if (kind == kKindMxf8) {
       const int fa = swap ? d->b_format : d->a_format, fb = swap ? d->a_format : d->b_format;
       p.idesc = make_idesc_block_scaled(fa == CPUOPS_B200_FMT_E5M2 ? 1u : 0u,
-                                        fb == CPUOPS_B200_FMT_E5M2 ? 1u : 0u, kTileM, ch.BN);
+                                        fb == CPUOPS_B200_FMT_E5M2 ? 1u : 0u, tile_m, ch.BN);
     } else {
-      p.idesc = make_idesc_block_scaled(1u, 1u, kTileM, ch.BN);  // e2m1 x e2m1
+      p.idesc = make_idesc_block_scaled(1u, 1u, tile_m, ch.BN);  // e2m1 x e2m1
     }
     p.mode = ch.slices > 1 ? kModePartial : kModeEpilogue;
     p.epi = epi;
@@ -1029,7 +1106,7 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
       p.clk_dbg = g_clk_buf;
     }
     const int sf_stage_bytes = p.sfa_stage_bytes + p.sfb_stage_bytes;
-    const int per_stage = gemm_stage_bytes(ch.BN) + sf_stage_bytes;
+    const int per_stage = gemm_stage_bytes(b_rows) + sf_stage_bytes;
     int stages = (st.smem_optin - 1024 - kBarrierBytes - (p.c_ring ? 1024 + kCRingBytes : 0)) / per_stage;
     stages = std::min({stages, kMaxStages, std::max(2, k_blocks)});
     if (stages < 2) {
@@ -1038,37 +1115,97 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     }
     p.stages = stages;
     // At least 120 KB so that two CTAs never share an SM: each allocates all of tensor memory.
-    const int smem = std::max(gemm_smem_bytes(ch.BN, stages, sf_stage_bytes, p.c_ring),
+    const int smem = std::max(gemm_smem_bytes(b_rows, stages, sf_stage_bytes, p.c_ring),
                               120 * 1024);
     const int64_t total_tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles * p.slices;
-    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(total_tiles, st.sm_count));
+    unsigned grid = static_cast<unsigned>(std::min<int64_t>(total_tiles, st.sm_count));
+    CUtensorMap tmSFA = tmA, tmSFB = tmA;  // used by the pair kernel's scale loads only
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = static_cast<size_t>(smem);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (ch.pair) {
+      attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+      attr[n_attr].val.clusterDim.x = 2;
+      attr[n_attr].val.clusterDim.y = 1;
+      attr[n_attr].val.clusterDim.z = 1;
+      ++n_attr;
+      if (st.pair_clusters[kind] < 0) {
+        cudaLaunchConfig_t probe = cfg;
+        probe.gridDim = dim3(2 * st.sm_count);
+        probe.dynamicSmemBytes = static_cast<size_t>(st.smem_optin);
+        probe.attrs = attr;
+        probe.numAttrs = 1;
+        int nc = 0;
+        cudaError_t e = cudaSuccess;
+        if (kind == kKindI8) {
+          e = cudaOccupancyMaxActiveClusters(&nc, gemm_tcgen05_kernel<kKindI8, true>, &probe);
+        } else if (kind == kKindMxf8) {
+          e = cudaOccupancyMaxActiveClusters(&nc, gemm_tcgen05_kernel<kKindMxf8, true>, &probe);
+        } else {
+          e = cudaOccupancyMaxActiveClusters(&nc, gemm_tcgen05_kernel<kKindMxf4, true>, &probe);
+        }
+        if (e != cudaSuccess) {
+          cudaGetLastError();
+          nc = 0;
+        }
+        st.pair_clusters[kind] = nc;
+      }
+      if (st.pair_clusters[kind] <= 0) {
+        set_error("internal: two-CTA clusters cannot be launched on this device");
+        return CPUOPS_B200_STATUS_CUDA_ERROR;
+      }
+      grid = 2u * static_cast<unsigned>(std::min<int64_t>(total_tiles, st.pair_clusters[kind]));
+      if (is_mx) {
+        if (int rc = make_tensor_map_atoms(&tmSFA, p.sfa, sfa_bytes / 512, p.sfa_stage_bytes / 512)) return rc;
+        if (int rc = make_tensor_map_atoms(&tmSFB, p.sfb, sfb_bytes / 512, p.sfb_stage_bytes / 512)) return rc;
+      }
+    }
+    cfg.gridDim = dim3(grid);
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     if (g_profile) {
       CUDA_TRY(cudaEventCreate(&ev0));
       CUDA_TRY(cudaEventCreate(&ev1));
       CUDA_TRY(cudaEventRecord(ev0, stream));
     }
-    if (kind == kKindI8) {
-      gemm_tcgen05_kernel<kKindI8><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, tmC, p);
-    } else {
+    if (is_mx && !g_profile) {
       // MX: the scale re-layout kernel is the launch just before this one.  Programmatic
       // stream serialization lets this kernel's CTAs start (barriers, tensor memory,
       // descriptor prefetch) while that one is still running; the producer thread waits
-      // for it before the first scale load.
-      cudaLaunchConfig_t cfg = {};
-      cfg.gridDim = dim3(grid);
-      cfg.blockDim = dim3(kGemmThreads);
-      cfg.dynamicSmemBytes = static_cast<size_t>(smem);
-      cfg.stream = stream;
-      cudaLaunchAttribute attr[1];
-      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-      attr[0].val.programmaticStreamSerializationAllowed = 1;
-      cfg.attrs = attr;
-      cfg.numAttrs = g_profile ? 0 : 1;  // timing events sit between the two launches
-      if (kind == kKindMxf8) {
-        CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<kKindMxf8>, tmA, tmB, tmC, p));
+      // for it before the first scale load.  (Not while profiling: the timing events sit
+      // between the two launches.)
+      attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+      ++n_attr;
+    }
+    g_last_plan.swapped = ch.swap ? 1 : 0;
+    g_last_plan.tile_n = ch.BN;
+    g_last_plan.pair = ch.pair ? 1 : 0;
+    g_last_plan.slices = ch.slices;
+    g_last_plan.stages = stages;
+    g_last_plan.grid = static_cast<int32_t>(grid);
+    g_last_plan.c_ring = p.c_ring;
+    cfg.attrs = attr;
+    cfg.numAttrs = n_attr;
+    if (kind == kKindI8) {
+      if (ch.pair) {
+        CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<kKindI8, true>, tmA, tmB, tmC, tmSFA, tmSFB, p));
       } else {
-        CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<kKindMxf4>, tmA, tmB, tmC, p));
+        CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<kKindI8, false>, tmA, tmB, tmC, tmSFA, tmSFB, p));
+      }
+    } else if (kind == kKindMxf8) {
+      if (ch.pair) {
+        CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<kKindMxf8, true>, tmA, tmB, tmC, tmSFA, tmSFB, p));
+      } else {
+        CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<kKindMxf8, false>, tmA, tmB, tmC, tmSFA, tmSFB, p));
+      }
+    } else {
+      if (ch.pair) {
+        CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<kKindMxf4, true>, tmA, tmB, tmC, tmSFA, tmSFB, p));
+      } else {
+        CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<kKindMxf4, false>, tmA, tmB, tmC, tmSFA, tmSFB, p));
       }
     }
     g_launches.fetch_add(1);
@@ -1160,7 +1297,7 @@ int noalloc_setup(int device, NoAllocDevice** out) {
     nd.scratch = static_cast<unsigned char*>(sym);
     CUDA_TRY(cudaDeviceGetAttribute(&nd.sm_count, cudaDevAttrMultiProcessorCount, device));
     CUDA_TRY(cudaDeviceGetAttribute(&nd.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
-    CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindI8>,
+    CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindI8, false>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, nd.smem_optin));
     if (!g_encode) {
       void* fn = nullptr;
@@ -1307,6 +1444,7 @@ CPUOPS_B200_API int cpuops_b200_gemm_i8_noalloc(const cpuops_b200_gemm_desc* d) 
   p.slices = slices;
   p.BN = BN;
   p.nacc = 2;
+  p.raster_m = 8;
   p.a_mn_major = a_kmajor ? 0 : 1;
   p.b_mn_major = b_kmajor ? 0 : 1;
   p.idesc = make_idesc(2 /*s32*/, 0u /*u8*/, 1u /*s8*/, p.a_mn_major, p.b_mn_major, kTileM, BN);
@@ -1328,7 +1466,8 @@ CPUOPS_B200_API int cpuops_b200_gemm_i8_noalloc(const cpuops_b200_gemm_desc* d) 
   const int smem = std::max(gemm_smem_bytes(BN, stages, 0), 120 * 1024);
   const int64_t total_tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles * p.slices;
   const unsigned grid = static_cast<unsigned>(std::min<int64_t>(total_tiles, nd->sm_count));
-  gemm_tcgen05_kernel<kKindI8><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, tmA /*unused: no C ring*/, p);
+  gemm_tcgen05_kernel<kKindI8, false><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, tmA /*unused: no C ring*/,
+                                                                            tmA, tmA /*unused: MX pair only*/, p);
   g_launches.fetch_add(1);
   CUDA_TRY(cudaGetLastError());
   const int64_t total = static_cast<int64_t>(m) * n;

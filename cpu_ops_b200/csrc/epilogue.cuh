@@ -81,6 +81,80 @@ __device__ __forceinline__ uint32_t apply_op_bits(const EpilogueOp& op, uint32_t
   }
 }
 
+// One chain op on a 32-column chunk of one accumulator row (registers r[0..32)).  The
+// opcode is uniform over the kernel, so it is dispatched once per chunk, outside the
+// element loop; a vector indexed by column is fetched as eight 16-byte loads (the same
+// addresses in every lane: one broadcast transaction each), a vector indexed by row as
+// one load.  Columns at or beyond `ncols` are computed on harmlessly and never stored.
+// The arithmetic per element is exactly apply_op_bits'.
+template <bool kInt>
+__device__ __forceinline__ void apply_op_chunk(const EpilogueOp& op, uint32_t (&r)[32], int krow,
+                                               int kcol0, int ncols) {
+  const int code = op.opcode;
+  if (code == kOpBiasAdd || code == kOpScalePerRow || code == kOpScalePerCol) {
+    uint32_t v[32];
+    const uint32_t* vec = static_cast<const uint32_t*>(op.ptr);
+    if (op.index_by_krow) {
+      const uint32_t x = __ldg(vec + krow);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = x;
+    } else if (ncols == 32 && (reinterpret_cast<uintptr_t>(vec + kcol0) & 15u) == 0) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        const uint4 q = __ldg(reinterpret_cast<const uint4*>(vec + kcol0 + i));
+        v[i] = q.x; v[i + 1] = q.y; v[i + 2] = q.z; v[i + 3] = q.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = i < ncols ? __ldg(vec + kcol0 + i) : 0u;
+    }
+    if constexpr (kInt) {
+      if (code == kOpBiasAdd) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] += v[i];
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] *= v[i];
+      }
+    } else {
+      if (code == kOpBiasAdd) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          r[i] = __float_as_uint(__fadd_rn(__uint_as_float(r[i]), __uint_as_float(v[i])));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          r[i] = __float_as_uint(__fmul_rn(__uint_as_float(r[i]), __uint_as_float(v[i])));
+      }
+    }
+  } else if (code == kOpRelu) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      if constexpr (kInt) {
+        r[i] = static_cast<int32_t>(r[i]) < 0 ? 0u : r[i];
+      } else {
+        r[i] = __uint_as_float(r[i]) < 0.0f ? 0u : r[i];  // x < 0 ? +0.0f : x (NaN and -0.0 pass)
+      }
+    }
+  } else if (code == kOpClamp) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      if constexpr (kInt) {
+        const int32_t lo = static_cast<int32_t>(op.lo), hi = static_cast<int32_t>(op.hi);
+        const int32_t x = static_cast<int32_t>(r[i]);
+        r[i] = static_cast<uint32_t>(x < lo ? lo : (hi < x ? hi : x));
+      } else {
+        const float lo = __uint_as_float(op.lo), hi = __uint_as_float(op.hi);
+        const float x = __uint_as_float(r[i]);
+        r[i] = __float_as_uint(x < lo ? lo : (hi < x ? hi : x));
+      }
+    }
+  } else if (code == kOpGelu || code == kOpSilu) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) r[i] = apply_op_bits<kInt>(op, r[i], krow, kcol0 + i);
+  }
+}
+
 // One element, all steps (used by the split-k reduce and k == 0 kernels).
 template <bool kInt>
 __device__ __forceinline__ uint32_t epilogue_element(const EpilogueParams& e, uint32_t acc,

@@ -26,20 +26,20 @@
 #include "epilogue.cuh"
 #include "gemm_params.h"
 #include "ptx_sm100.cuh"
+#include "ptx_sm100_pair.cuh"
 
 namespace b200 {
 
 constexpr int kGemmThreads = 224;  // producer, MMA issuer, 4 epilogue warps, scale copier
 constexpr uint32_t kTmemCols = 512;
-constexpr int kRasterGroupM = 8;
 
 struct TileCoord {
   int m_tile, n_tile, slice, kb0, nkb;
 };
 
 // Work item -> (m tile, n tile, k slice).  Tiles are walked in groups of
-// kRasterGroupM m-tiles (m fastest) so that the CTAs running at any moment
-// share B tiles and a narrow band of A in L2.  k-slices are balanced contiguous
+// p.raster_m m-tiles (m fastest) so that the CTAs running at any moment share a
+// band of A and a band of B of about the same size in L2.  k-slices are balanced contiguous
 // ranges of 128-byte k-blocks, like the CPU library's split_range
 // (gemm/threadblock/threadblock_swizzle.h:31-37).
 __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int t) {
@@ -47,10 +47,10 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int t) {
   const int mn = p.m_tiles * p.n_tiles;
   c.slice = t / mn;
   const int r = t - c.slice * mn;
-  const int per_group = kRasterGroupM * p.n_tiles;
+  const int per_group = p.raster_m * p.n_tiles;
   const int g = r / per_group;
-  const int first_m = g * kRasterGroupM;
-  const int gsize = min(kRasterGroupM, p.m_tiles - first_m);
+  const int first_m = g * p.raster_m;
+  const int gsize = min(p.raster_m, p.m_tiles - first_m);
   const int in = r - g * per_group;
   c.m_tile = first_m + in % gsize;
   c.n_tile = in / gsize;
@@ -118,12 +118,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[3
   }
 #pragma unroll
   for (int i = 0; i < 32; ++i) r[i] = linear_combine_bits<kInt>(e, r[i], src[i]);
-  for (int t = 0; t < e.n_ops; ++t) {
-    const EpilogueOp op = e.ops[t];
-#pragma unroll
-    for (int i = 0; i < 32; ++i)
-      if (i < ncols) r[i] = apply_op_bits<kInt>(op, r[i], krow, kcol0 + i);
-  }
+  for (int t = 0; t < e.n_ops; ++t) apply_op_chunk<kInt>(e.ops[t], r, krow, kcol0, ncols);
   uint32_t* d = static_cast<uint32_t*>(e.D) + (krow * e.d_sr + kcol0 * e.d_sc);
   if (e.d_sc == 1 && ncols == 32 && aligned16(d)) {
 #pragma unroll
@@ -136,13 +131,26 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[3
   }
 }
 
-template <int KIND>
+// kPair: launched as clusters of two CTAs; the pair computes 256-row tiles with the
+// cta_group::2 instructions (see ptx_sm100_pair.cuh).  CTA rank r of a pair stages
+// rows [128 r, 128 r + 128) of the A tile and rows [r BN/2, (r + 1) BN/2) of the B
+// tile, all loads credit the leader's full barrier, the leader's MMA thread frees the
+// stage in both CTAs with a multicast commit, and each CTA's epilogue warps drain their
+// own 128 accumulator rows.  p.m_tiles counts 256-row tiles in that case.
+template <int KIND, bool kPair>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                         const __grid_constant__ CUtensorMap tmB,
-                        const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+                        const __grid_constant__ CUtensorMap tmC,
+                        const __grid_constant__ CUtensorMap tmSFA,
+                        const __grid_constant__ CUtensorMap tmSFB, const GemmParams p) {
   constexpr bool kInt = (KIND == kKindI8);
   constexpr bool kMx = !kInt;
+  constexpr int kCtas = kPair ? 2 : 1;
+  const uint32_t cta_rank = kPair ? cluster_cta_rank() : 0u;
+  const bool leader = cta_rank == 0;
+  const int work0 = static_cast<int>(blockIdx.x) / kCtas;      // first work item of this CTA (pair)
+  const int work_step = static_cast<int>(gridDim.x) / kCtas;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -152,7 +160,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int stages = p.stages;
-  const int stage_bytes = gemm_stage_bytes(p.BN);
+  const int b_rows = p.BN / kCtas;  // rows of the B tile staged by this CTA
+  const int stage_bytes = gemm_stage_bytes(b_rows);
   // Each stage also carries the k-block's scale factors (MX), in a separate region so
   // that the operand tiles stay 1024-byte aligned.
   const int sf_stage = p.sfa_stage_bytes + p.sfb_stage_bytes;
@@ -179,7 +188,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full_bar(b), 1);   // tcgen05.commit after the tile's last MMA
-      mbar_init(acc_empty_bar(b), 4);  // one arrival per epilogue warp
+      mbar_init(acc_empty_bar(b), 4 * kCtas);  // one arrival per epilogue warp (of both CTAs)
     }
     mbar_init(drain_bar, 1);
     mbar_init(sf_drain_bar, 1);
@@ -187,18 +196,26 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     for (int w = 0; w < 4; ++w)
       for (int b = 0; b < 2; ++b) mbar_init(c_full_bar(w, b), 1);  // TMA load of one C chunk
     *abort_flag = 0;
-    fence_mbar_init();
+    if constexpr (kPair) {
+      fence_mbar_init_cluster();
+    } else {
+      fence_mbar_init();
+    }
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
-    tmem_relinquish();
+    tmem_alloc_g<kPair>(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish_g<kPair>();
   }
   if (warp == 0 && lane == 0) {
     prefetch_tensormap(&tmA);
     prefetch_tensormap(&tmB);
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (kPair) {
+    cluster_sync_all();  // the peer's barriers are initialised before anything targets them
+  } else {
+    __syncthreads();
+  }
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -225,54 +242,81 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
+    // The whole warp runs the loop; one elected lane issues (see the MMA issuer below).
+    {
+      const uint32_t el = elect_one() ? 1u : 0u;
       int s = 0;
-      uint32_t ph = 0, armed = 0, armed_parity = 0;
+      uint32_t ph = 0, armed = 0, armed_parity = 0, peek = 0;
       bool ok = true;
       const uint32_t tx_bytes = static_cast<uint32_t>(stage_bytes + sf_stage);
-      const uint32_t full0 = full_bar(0), empty0 = empty_bar(0);
+      // pair: every load of both CTAs credits the leader's barrier, which alone is armed
+      // (by the leader's producer) with the bytes of both
+      const uint32_t full0 = kPair ? map_to_cta(full_bar(0), 0) : full_bar(0), empty0 = empty_bar(0);
+      const uint32_t tx_total = tx_bytes * kCtas;
       uint32_t full_addr = full0, empty_addr = empty0, a_dst = smem_base, sf_dst = sf_base;
-      const int a_mn = p.a_mn_major, b_mn = p.b_mn_major, b_chunks = p.BN / 128;
+      const int a_mn = p.a_mn_major, b_mn = p.b_mn_major, b_chunks = b_rows / 128;
+      const int sfa_atoms_ld = p.sfa_stage_bytes / 512, sfb_atoms_ld = p.sfb_stage_bytes / 512;
       const uint32_t sfa_bytes = p.sfa_stage_bytes, sfb_bytes = p.sfb_stage_bytes;
       // The scale atoms come from the re-layout kernel launched just before this one,
       // which may still be running (programmatic stream serialization).
       if constexpr (kMx) asm volatile("griddepcontrol.wait;" ::: "memory");
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = work0; t < total_tiles && ok; t += work_step) {
         const TileCoord tc = decode_tile(p, t);
-        const int m0 = tc.m_tile * kTileM, n0 = tc.n_tile * p.BN;
+        const int m_tile128 = tc.m_tile * kCtas + static_cast<int>(cta_rank);  // this CTA's 128 rows
+        const int m0 = m_tile128 * kTileM;
+        const int n0 = tc.n_tile * p.BN + static_cast<int>(cta_rank) * b_rows;  // this CTA's B rows
         int kx = tc.kb0 * 128;  // k coordinate (bytes along k) of the next block
         const uint8_t* sfa_src = nullptr;
         const uint8_t* sfb_src = nullptr;
+        int sfa_atom = 0, sfb_atom = 0;  // pair: atom (row) index in the scale tensor maps
         if constexpr (kMx) {
-          sfa_src = p.sfa + (static_cast<int64_t>(tc.m_tile) * p.k_blocks + tc.kb0) * p.sfa_stage_bytes;
+          sfa_src = p.sfa + (static_cast<int64_t>(m_tile128) * p.k_blocks + tc.kb0) * p.sfa_stage_bytes;
           sfb_src = p.sfb + (static_cast<int64_t>(tc.n_tile) * p.k_blocks + tc.kb0) * p.sfb_stage_bytes;
+          sfa_atom = (m_tile128 * p.k_blocks + tc.kb0) * sfa_atoms_ld;
+          sfb_atom = (tc.n_tile * p.k_blocks + tc.kb0) * sfb_atoms_ld;
         }
         for (int i = 0; i < tc.nkb; ++i, kx += 128) {
-          if (!mbar_wait_bounded(empty_addr, ph ^ 1u, abort_flag)) {
-            record_error(p, abort_flag, kErrProducerWait);
+          if (!peek && !__all_sync(0xffffffffu, mbar_wait_bounded(empty_addr, ph ^ 1u, abort_flag))) {
+            if (el) record_error(p, abort_flag, kErrProducerWait);
             ok = false;
             break;
           }
-          mbar_expect_tx(full_addr, tx_bytes);
-          armed |= 1u << s;
-          armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
+          {
+            // probe the next stage's barrier now; the answer is used on the next trip
+            const bool wrap = s + 1 == stages;
+            peek = __all_sync(0xffffffffu, mbar_test_wait(wrap ? empty0 : empty_addr + 8,
+                                                         (wrap ? (ph ^ 1u) : ph) ^ 1u)) ? 1u : 0u;
+          }
+          if (leader) {
+            mbar_expect_tx_p(full_bar(s), tx_total, el);
+            armed |= 1u << s;
+            armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
+          }
           const uint32_t b_dst = a_dst + kTileM * 128;
           if (!a_mn) {
-            tma_load_2d(a_dst, &tmA, full_addr, kx, m0);
+            tma_load_2d_g<kPair>(a_dst, &tmA, full_addr, kx, m0, el);
           } else {
-            tma_load_2d(a_dst, &tmA, full_addr, m0, kx);
+            tma_load_2d_g<kPair>(a_dst, &tmA, full_addr, m0, kx, el);
           }
           if (!b_mn) {
-            tma_load_2d(b_dst, &tmB, full_addr, kx, n0);
+            tma_load_2d_g<kPair>(b_dst, &tmB, full_addr, kx, n0, el);
           } else {
             for (int c = 0; c < b_chunks; ++c)
-              tma_load_2d(b_dst + c * 16384, &tmB, full_addr, n0 + c * 128, kx);
+              tma_load_2d_g<kPair>(b_dst + c * 16384, &tmB, full_addr, n0 + c * 128, kx, el);
           }
           if constexpr (kMx) {
-            bulk_load(sf_dst, sfa_src, sfa_bytes, full_addr);
-            bulk_load(sf_dst + sfa_bytes, sfb_src, sfb_bytes, full_addr);
-            sfa_src += sfa_bytes;
-            sfb_src += sfb_bytes;
+            if constexpr (kPair) {
+              // rows of 512 bytes (one atom each) of the re-laid-out scale arrays
+              tma_load_2d_g<true>(sf_dst, &tmSFA, full_addr, 0, sfa_atom, el);
+              tma_load_2d_g<true>(sf_dst + sfa_bytes, &tmSFB, full_addr, 0, sfb_atom, el);
+              sfa_atom += sfa_atoms_ld;
+              sfb_atom += sfb_atoms_ld;
+            } else {
+              bulk_load_p(sf_dst, sfa_src, sfa_bytes, full_addr, el);
+              bulk_load_p(sf_dst + sfa_bytes, sfb_src, sfb_bytes, full_addr, el);
+              sfa_src += sfa_bytes;
+              sfb_src += sfb_bytes;
+            }
           }
           if (++s == stages) {
             s = 0;
@@ -289,11 +333,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
         }
       }
-      if (*abort_flag != 0) {
+      if (*abort_flag != 0 && el) {
         // Let copies that were already issued land before the CTA exits.
         int dummy = 0;
         for (int st = 0; st < stages; ++st)
           if (armed & (1u << st)) mbar_wait_bounded(full_bar(st), (armed_parity >> st) & 1u, &dummy);
+        if constexpr (kPair) {
+          // the peer cannot watch the leader's barriers: give its copies time to land
+          if (!leader) {
+            const uint64_t t_end = global_timer_ns() + 100000;
+            while (global_timer_ns() < t_end) __nanosleep(1000);
+          }
+        }
       }
     }
     __syncwarp();
@@ -302,8 +353,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     // One thread feeds the tensor pipe.  A 128 x 256 x 32-byte MMA executes in 128
     // cycles, so this thread has about that much time per instruction: the loop
     // keeps every descriptor as a running 32-bit word and does no divisions,
-    // 64-bit arithmetic or parameter re-loads.
-    if (lane == 0) {
+    // 64-bit arithmetic or parameter re-loads.  In a pair only the leader issues.
+    // The whole warp runs the loop in lock step and one elected lane issues: with
+    // converged control flow the descriptors live in uniform registers, which is what
+    // the tcgen05 instructions take, and the per-instruction cost stays well below the
+    // MMA's execution time (a loop run by one lane under a divergent branch did not).
+    if (leader) {
+      const uint32_t el = elect_one() ? 1u : 0u;
+      constexpr uint32_t kAll = 0xffffffffu;
       bool ok = true;
       // Matrix descriptors.  K-major: rows of 128 bytes, 8-row groups 1024 bytes
       // apart.  MN-major: the 128-byte rows run along m/n and k advances by rows; a
@@ -337,11 +394,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       int s = 0, buf = 0;
       uint32_t ph = 0, acc_ph = 0, peek = 0;
       uint32_t a_lo = a_lo0, b_lo = b_lo0, full_addr = full0, empty_addr = empty0;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = work0; t < total_tiles && ok; t += work_step) {
         const TileCoord tc = decode_tile(p, t);
         long long tw0 = dbg ? clock64() : 0;
-        if (!mbar_wait_bounded(acc_empty_bar(buf), acc_ph ^ 1u, abort_flag)) {
-          record_error(p, abort_flag, kErrMmaWaitAcc);
+        if (!__all_sync(kAll, mbar_wait_bounded(acc_empty_bar(buf), acc_ph ^ 1u, abort_flag))) {
+          if (el) record_error(p, abort_flag, kErrMmaWaitAcc);
           break;
         }
         if (dbg) dbg_wait_acc += clock64() - tw0;
@@ -350,8 +407,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         uint32_t accumulate = 0;
         for (int i = 0; i < tc.nkb; ++i) {
           tw0 = dbg ? clock64() : 0;
-          if (!peek && !mbar_wait_bounded(full_addr, ph, abort_flag)) {
-            record_error(p, abort_flag, kErrMmaWaitFull);
+          if (!peek && !__all_sync(kAll, mbar_wait_bounded(full_addr, ph, abort_flag))) {
+            if (el) record_error(p, abort_flag, kErrMmaWaitFull);
             ok = false;
             break;
           }
@@ -360,39 +417,40 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           // MMAs have been issued
           const uint32_t nfull = (s + 1 == stages) ? full0 : full_addr + 8;
           const uint32_t nph = (s + 1 == stages) ? (ph ^ 1u) : ph;
-          peek = mbar_test_wait(nfull, nph);
+          peek = __all_sync(kAll, mbar_test_wait(nfull, nph)) ? 1u : 0u;
           const uint32_t sfb_t = sfa_t + 4u * sfa_atoms;
           if constexpr (kMx) {
             // the k-block's scale factors, copied into this slot by the scale copier
             tw0 = dbg ? clock64() : 0;
-            if (!peek_sf && !mbar_wait_bounded(sf_full_bar(sf_q), sf_ph, abort_flag)) {
-              record_error(p, abort_flag, kErrMmaWaitFull);
+            if (!peek_sf && !__all_sync(kAll, mbar_wait_bounded(sf_full_bar(sf_q), sf_ph, abort_flag))) {
+              if (el) record_error(p, abort_flag, kErrMmaWaitFull);
               ok = false;
               break;
             }
             if (dbg) dbg_wait_sf += clock64() - tw0;
             const bool wrap = sf_q + 1 == sf_slots;
-            peek_sf = mbar_test_wait(sf_full_bar(wrap ? 0u : sf_q + 1), wrap ? (sf_ph ^ 1u) : sf_ph);
+            peek_sf = __all_sync(kAll, mbar_test_wait(sf_full_bar(wrap ? 0u : sf_q + 1),
+                                                      wrap ? (sf_ph ^ 1u) : sf_ph)) ? 1u : 0u;
           }
           tc_fence_after_sync();
           if constexpr (KIND == kKindI8) {
-            mma_i8_w(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc, accumulate);
-            mma_i8_w(d_tmem, a_lo + a_k, a_hi, b_lo + b_k, b_hi, idesc, 1u);
-            mma_i8_w(d_tmem, a_lo + 2 * a_k, a_hi, b_lo + 2 * b_k, b_hi, idesc, 1u);
-            mma_i8_w(d_tmem, a_lo + 3 * a_k, a_hi, b_lo + 3 * b_k, b_hi, idesc, 1u);
+            mma_i8_g<kPair>(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc, accumulate, el);
+            mma_i8_g<kPair>(d_tmem, a_lo + a_k, a_hi, b_lo + b_k, b_hi, idesc, 1u, el);
+            mma_i8_g<kPair>(d_tmem, a_lo + 2 * a_k, a_hi, b_lo + 2 * b_k, b_hi, idesc, 1u, el);
+            mma_i8_g<kPair>(d_tmem, a_lo + 3 * a_k, a_hi, b_lo + 3 * b_k, b_hi, idesc, 1u, el);
           } else if constexpr (KIND == kKindMxf8) {
-            mma_mxf8f6f4_w(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc, sfa_t, sfb_t, accumulate);
-            mma_mxf8f6f4_w(d_tmem, a_lo + 2, a_hi, b_lo + 2, b_hi, id1, sfa_t, sfb_t, 1u);
-            mma_mxf8f6f4_w(d_tmem, a_lo + 4, a_hi, b_lo + 4, b_hi, id2, sfa_t, sfb_t, 1u);
-            mma_mxf8f6f4_w(d_tmem, a_lo + 6, a_hi, b_lo + 6, b_hi, id3, sfa_t, sfb_t, 1u);
+            mma_mxf8f6f4_g<kPair>(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc, sfa_t, sfb_t, accumulate, el);
+            mma_mxf8f6f4_g<kPair>(d_tmem, a_lo + 2, a_hi, b_lo + 2, b_hi, id1, sfa_t, sfb_t, 1u, el);
+            mma_mxf8f6f4_g<kPair>(d_tmem, a_lo + 4, a_hi, b_lo + 4, b_hi, id2, sfa_t, sfb_t, 1u, el);
+            mma_mxf8f6f4_g<kPair>(d_tmem, a_lo + 6, a_hi, b_lo + 6, b_hi, id3, sfa_t, sfb_t, 1u, el);
           } else {
-            mma_mxf4_w(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc, sfa_t, sfb_t, accumulate);
-            mma_mxf4_w(d_tmem, a_lo + 2, a_hi, b_lo + 2, b_hi, id1, sfa_t, sfb_t, 1u);
-            mma_mxf4_w(d_tmem, a_lo + 4, a_hi, b_lo + 4, b_hi, id2, sfa_t + sfa_half, sfb_t + sfb_half, 1u);
-            mma_mxf4_w(d_tmem, a_lo + 6, a_hi, b_lo + 6, b_hi, id3, sfa_t + sfa_half, sfb_t + sfb_half, 1u);
+            mma_mxf4_g<kPair>(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc, sfa_t, sfb_t, accumulate, el);
+            mma_mxf4_g<kPair>(d_tmem, a_lo + 2, a_hi, b_lo + 2, b_hi, id1, sfa_t, sfb_t, 1u, el);
+            mma_mxf4_g<kPair>(d_tmem, a_lo + 4, a_hi, b_lo + 4, b_hi, id2, sfa_t + sfa_half, sfb_t + sfb_half, 1u, el);
+            mma_mxf4_g<kPair>(d_tmem, a_lo + 6, a_hi, b_lo + 6, b_hi, id3, sfa_t + sfa_half, sfb_t + sfb_half, 1u, el);
           }
           accumulate = 1u;
-          tc_commit(empty_addr);  // frees the stage once these MMAs (and copies) have read it
+          tc_commit_both<kPair>(empty_addr, el);  // frees the stage (in both CTAs) once these MMAs have read it
           if constexpr (kMx) {
             sfa_t += sf_cols;
             if (++sf_q == sf_slots) {
@@ -415,17 +473,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             empty_addr += 8;
           }
         }
-        if (ok) tc_commit(acc_full_bar(buf));
+        if (ok) tc_commit_both<kPair>(acc_full_bar(buf), el);
         if (++buf == nacc) {
           buf = 0;
           acc_ph ^= 1u;
         }
       }
       // Nothing may still be executing when tensor memory is released.
-      tc_commit(drain_bar);
+      tc_commit_g<kPair>(drain_bar, el);
       int dummy = 0;
-      if (!mbar_wait_bounded(drain_bar, 0, &dummy)) record_error(p, abort_flag, kErrDrainWait);
-      if (dbg) {
+      if (!__all_sync(kAll, mbar_wait_bounded(drain_bar, 0, &dummy)) && el)
+        record_error(p, abort_flag, kErrDrainWait);
+      if (dbg && el) {
         p.clk_dbg[2] = static_cast<unsigned long long>(clock64() - dbg_start);
         p.clk_dbg[3] = static_cast<unsigned long long>(dbg_wait_full);
         p.clk_dbg[4] = static_cast<unsigned long long>(dbg_wait_acc);
@@ -439,7 +498,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     // last read the target slot are done, copy the atoms shared -> tensor memory and let
     // tcgen05.commit announce them on the slot's barrier.
     if constexpr (kMx) {
-      if (lane == 0) {
+      if (leader) {
+        const uint32_t el = elect_one() ? 1u : 0u;
+        constexpr uint32_t kAll = 0xffffffffu;
         const uint32_t sf_hi = static_cast<uint32_t>(sf_hi64 >> 32);
         const uint32_t sf_lo0 = static_cast<uint32_t>(sf_hi64) | (sf_base >> 4);
         const uint32_t sf_step = static_cast<uint32_t>(sf_stage) >> 4;
@@ -452,17 +513,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         uint32_t ph = 0, fph = 0, q = 0, it = 0, peek_full = 0;
         uint32_t sf_lo = sf_lo0, dst0 = sf_t0;
         bool ok = true;
-        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        for (int t = work0; t < total_tiles && ok; t += work_step) {
           const TileCoord tc = decode_tile(p, t);
           for (int i = 0; i < tc.nkb; ++i, ++it) {
-            if (!peek_full && !mbar_wait_bounded(full_bar(s), ph, abort_flag)) {
-              record_error(p, abort_flag, kErrMmaWaitFull);
+            if (!peek_full && !__all_sync(kAll, mbar_wait_bounded(full_bar(s), ph, abort_flag))) {
+              if (el) record_error(p, abort_flag, kErrMmaWaitFull);
               ok = false;
               break;
             }
             if (need_free && it >= sf_slots) {
-              if (!mbar_wait_bounded(empty_bar(fs), fph, abort_flag)) {
-                record_error(p, abort_flag, kErrMmaWaitFull);
+              if (!__all_sync(kAll, mbar_wait_bounded(empty_bar(fs), fph, abort_flag))) {
+                if (el) record_error(p, abort_flag, kErrMmaWaitFull);
                 ok = false;
                 break;
               }
@@ -473,13 +534,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             }
             {
               const int ns = (s + 1 == stages) ? 0 : s + 1;
-              peek_full = mbar_test_wait(full_bar(ns), ns == 0 ? (ph ^ 1u) : ph);
+              peek_full = __all_sync(kAll, mbar_test_wait(full_bar(ns), ns == 0 ? (ph ^ 1u) : ph)) ? 1u : 0u;
             }
             tc_fence_after_sync();
             uint32_t src = sf_lo, dst = dst0;
-            for (uint32_t a = 0; a < sf_atoms; ++a, src += 32, dst += 4)
-              tmem_cp_32x128b_warpx4_w(dst, src, sf_hi);
-            tc_commit(sf_full_bar(q));
+            const uint32_t n_cp = (p.debug_flags & 8) ? (sf_atoms > 1 ? 1u : 0u) : sf_atoms;  // experiments
+            for (uint32_t a = 0; a < n_cp; ++a, src += 32, dst += 4)
+              tmem_cp_atom_g<kPair>(dst, src, sf_hi, el);
+            tc_commit_g<kPair>(sf_full_bar(q), el);
             if (++q == sf_slots) {
               q = 0;
               dst0 = sf_t0;
@@ -496,9 +558,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
         }
         // no copy may be in flight when tensor memory is released
-        tc_commit(sf_drain_bar);
+        tc_commit_g<kPair>(sf_drain_bar, el);
         int dummy = 0;
-        if (!mbar_wait_bounded(sf_drain_bar, 0, &dummy)) record_error(p, abort_flag, kErrDrainWait);
+        if (!__all_sync(kAll, mbar_wait_bounded(sf_drain_bar, 0, &dummy)) && el)
+          record_error(p, abort_flag, kErrDrainWait);
       }
     }
     __syncwarp();
@@ -517,11 +580,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const bool edbg = p.clk_dbg != nullptr && blockIdx.x == 0 && warp == 2 && lane == 0;
     long long edbg_wait = 0;
     const long long edbg_start = edbg ? clock64() : 0;
-    for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x, ++it) {
+    // pair: the leader's MMA thread waits for the epilogue warps of both CTAs
+    const uint32_t acc_empty0 = kPair ? map_to_cta(acc_empty_bar(0), 0) : acc_empty_bar(0);
+    for (int t = work0; t < total_tiles && alive; t += work_step, ++it) {
       const TileCoord tc = decode_tile(p, t);
       const int buf = it % nacc;
       const uint32_t acc_ph = static_cast<uint32_t>(it / nacc) & 1u;
-      const int row0 = tc.m_tile * kTileM + q * 32;
+      const int row0 = (tc.m_tile * kCtas + static_cast<int>(cta_rank)) * kTileM + q * 32;
       const int krow = row0 + lane;
       const int n0 = tc.n_tile * p.BN;
       if (ring && lane == 0) {
@@ -551,7 +616,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           // the accumulator is in registers: hand the buffer back to the MMA warp
           tc_fence_before_sync();
           __syncwarp();
-          if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+          if (lane == 0) {
+            if constexpr (kPair) {
+              mbar_arrive_cluster(acc_empty0 + 8u * buf);
+            } else {
+              mbar_arrive(acc_empty_bar(buf));
+            }
+          }
         }
         const int kcol0 = n0 + c * 32;
         const uint32_t* c_row = nullptr;
@@ -595,8 +666,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     p.clk_dbg[1] = global_timer_ns() - dbg_t0;
   }
   tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if constexpr (kPair) {
+    // neither CTA may leave (or release tensor memory) while the other can still touch
+    // its shared memory, barriers or accumulator
+    cluster_sync_all();
+  } else {
+    __syncthreads();
+  }
+  if (warp == 1) tmem_dealloc_g<kPair>(tmem_base, kTmemCols);
   if (p.clk_dbg != nullptr && threadIdx.x == 0) atomicMax(p.clk_dbg + 9, global_timer_ns());
 }
 

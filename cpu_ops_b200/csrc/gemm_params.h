@@ -62,6 +62,7 @@ struct GemmParams {
   int32_t BN;               // N tile (multiple of 32, <= 256)
   int32_t stages;           // smem pipeline depth
   int32_t nacc;             // TMEM accumulator buffers (1 or 2)
+  int32_t raster_m;         // m-tiles per raster group (tile walk order)
   int32_t a_mn_major, b_mn_major;
   uint32_t idesc;           // instruction descriptor without scale-factor ids
   int32_t mode;             // kModeEpilogue | kModePartial

@@ -85,6 +85,10 @@ enum { CPUOPS_B200_MEM_AUTO = 0, CPUOPS_B200_MEM_HOST = 1, CPUOPS_B200_MEM_DEVIC
 #define CPUOPS_B200_FLAG_ASYNC 1u /* device operands only: enqueue on `stream` and return \
                                      without synchronising; device-side errors are then   \
                                      reported by cpuops_b200_stream_status()              */
+/* Testing/tuning, like tile_n: force or forbid the two-CTA form of the kernel (a cluster
+ * of two CTAs per 256-row tile).  Neither flag: the library decides by problem size. */
+#define CPUOPS_B200_FLAG_PAIR_ON 2u
+#define CPUOPS_B200_FLAG_PAIR_OFF 4u
 
 typedef union cpuops_b200_scalar {
   int32_t i32; /* int8 path: alpha/beta/clamp bounds are s32 */
@@ -210,6 +214,20 @@ CPUOPS_B200_API int cpuops_b200_stream_status(void* stream);
  * summed device time and the number of timed launches, and forgets them. */
 CPUOPS_B200_API int cpuops_b200_profile(int enable);
 CPUOPS_B200_API int cpuops_b200_profile_collect(double* total_ms, int32_t* launches);
+
+/* What the last cpuops_b200_gemm call of this process that reached the tensor-core kernel
+ * launched (diagnostics for tests and benchmarks): */
+typedef struct cpuops_b200_plan {
+  int32_t swapped;   /* 1: the caller's B went on the MMA M side (small m)          */
+  int32_t tile_n;    /* N tile                                                    */
+  int32_t pair;      /* 1: two-CTA clusters, 256-row tiles                         */
+  int32_t slices;    /* split-k slices                                            */
+  int32_t stages;    /* shared-memory pipeline depth                              */
+  int32_t grid;      /* CTAs launched                                             */
+  int32_t c_ring;    /* 1: C prefetched by TMA into shared memory                  */
+  int32_t reserved;
+} cpuops_b200_plan;
+CPUOPS_B200_API int cpuops_b200_last_plan(cpuops_b200_plan* out);
 
 /* Kernels launched by this library in this process so far (all threads). */
 CPUOPS_B200_API uint64_t cpuops_b200_launch_count(void);

@@ -14,10 +14,10 @@ def layout(row_major):
 
 
 def run_int8_gpu(P, alpha=1, beta=0, relu=False, chain=(), split=0, tile_n=0, D=None, in_place=False,
-                 bufs=None):
+                 bufs=None, pair=None):
     """P: workloads.Int8Problem.  Returns (status, D)."""
     op = c.GemmU8S8S32(layout(P.a_row_major), layout(P.b_row_major), layout(P.c_row_major),
-                       tile_n=tile_n)
+                       tile_n=tile_n, pair=pair)
     if D is None:
         D = P.C.copy() if in_place else np.full_like(P.C, INT32_MIN)  # poison: all must be written
     Cbuf = D if in_place else P.C
@@ -38,8 +38,9 @@ def run_int8_oracle(oracle, P, alpha=1, beta=0, relu=False, ops=()):
     return D
 
 
-def run_mx_gpu(P, alpha=1.0, beta=0.0, relu=False, chain=(), split=0, tile_n=0, in_place=False):
-    op = c.GemmMx(STORAGE[P.fmt_a], STORAGE[P.fmt_b], layout(P.c_row_major), tile_n=tile_n)
+def run_mx_gpu(P, alpha=1.0, beta=0.0, relu=False, chain=(), split=0, tile_n=0, in_place=False,
+               pair=None):
+    op = c.GemmMx(STORAGE[P.fmt_a], STORAGE[P.fmt_b], layout(P.c_row_major), tile_n=tile_n, pair=pair)
     D = P.C.copy() if in_place else np.full_like(P.C, np.nan)   # NaN poison
     Cbuf = D if in_place else P.C
     epi = c.LinearCombinationFused(alpha, beta, list(chain),
