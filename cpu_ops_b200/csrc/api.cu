@@ -1084,7 +1084,7 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
       p.sfa_stage_bytes = (bps / 4) * 512;
       p.sfb_stage_bytes = (bps / 4) * ((ch.BN + 127) / 128) * 512;
       const int sf_cols = (p.sfa_stage_bytes + p.sfb_stage_bytes) / 512 * 4;
-      if (ch.nacc * ch.BN + sf_cols > 512) {
+      if (ch.nacc * ch.BN + 2 * sf_cols > 512) {  // the kernel rotates over at least two scale slots
         set_error("internal: tensor memory over-committed (BN %d)", ch.BN);
         return CPUOPS_B200_STATUS_CUDA_ERROR;
       }

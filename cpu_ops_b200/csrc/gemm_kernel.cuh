@@ -30,7 +30,7 @@
 
 namespace b200 {
 
-constexpr int kGemmThreads = 224;  // producer, MMA issuer, 4 epilogue warps, scale copier
+constexpr int kGemmThreads = 192;  // producer, MMA issuer, 4 epilogue warps
 constexpr uint32_t kTmemCols = 512;
 
 struct TileCoord {
@@ -175,8 +175,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * kMaxStages + 2 + b); };
   const uint32_t drain_bar = bar_base + 8u * (2 * kMaxStages + 4);
   auto c_full_bar = [&](int w, int b) { return bar_base + 8u * (2 * kMaxStages + 5 + w * 2 + b); };
-  auto sf_full_bar = [&](uint32_t q) { return bar_base + 8u * (40u + q); };  // 8 slots
-  const uint32_t sf_drain_bar = bar_base + 8u * 48u;
   uint32_t* tmem_slot =
       reinterpret_cast<uint32_t*>(smem + (bar_base - smem_base) + 8 * (2 * kMaxStages + 5 + 8));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -191,8 +189,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       mbar_init(acc_empty_bar(b), 4 * kCtas);  // one arrival per epilogue warp (of both CTAs)
     }
     mbar_init(drain_bar, 1);
-    mbar_init(sf_drain_bar, 1);
-    for (uint32_t q = 0; q < 8; ++q) mbar_init(sf_full_bar(q), 1);  // tcgen05.commit of the scale copies
     for (int w = 0; w < 4; ++w)
       for (int b = 0; b < 2; ++b) mbar_init(c_full_bar(w, b), 1);  // TMA load of one C chunk
     *abort_flag = 0;
@@ -223,8 +219,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const int nacc = p.nacc;
   // MX: the tensor-memory columns left over after the accumulators hold a ring of
   // scale-factor slots (one k-block each: the A atoms, then the B atoms, 4 columns per
-  // atom).  A dedicated thread fills them; copies issued by the MMA thread itself
-  // execute in line with its MMAs and cost the tensor pipe ~90 cycles each.
+  // atom).  The MMA warp copies a k-block's atoms shared -> tensor memory right before
+  // that k-block's MMAs; the tensor pipe runs both in issue order and the copies overlap
+  // the MMAs ahead of them.  Rotating over at least two slots keeps a copy from
+  // overwriting scales that the previous k-block's MMAs are still reading.
   const uint32_t sfa_atoms = p.sfa_stage_bytes / 512, sfb_atoms = p.sfb_stage_bytes / 512;
   const uint32_t sf_atoms = sfa_atoms + sfb_atoms;
   const uint32_t sf_cols = 4u * sf_atoms;
@@ -252,7 +250,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       // pair: every load of both CTAs credits the leader's barrier, which alone is armed
       // (by the leader's producer) with the bytes of both
       const uint32_t full0 = kPair ? map_to_cta(full_bar(0), 0) : full_bar(0), empty0 = empty_bar(0);
-      const uint32_t tx_total = tx_bytes * kCtas;
       uint32_t full_addr = full0, empty_addr = empty0, a_dst = smem_base, sf_dst = sf_base;
       const int a_mn = p.a_mn_major, b_mn = p.b_mn_major, b_chunks = b_rows / 128;
       const int sfa_atoms_ld = p.sfa_stage_bytes / 512, sfb_atoms_ld = p.sfb_stage_bytes / 512;
@@ -266,14 +263,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         const int m0 = m_tile128 * kTileM;
         const int n0 = tc.n_tile * p.BN + static_cast<int>(cta_rank) * b_rows;  // this CTA's B rows
         int kx = tc.kb0 * 128;  // k coordinate (bytes along k) of the next block
-        const uint8_t* sfa_src = nullptr;
-        const uint8_t* sfb_src = nullptr;
-        int sfa_atom = 0, sfb_atom = 0;  // pair: atom (row) index in the scale tensor maps
+        const uint8_t* sfa_base = nullptr;  // this tile's scale atoms, k-block 0
+        const uint8_t* sfb_base = nullptr;
         if constexpr (kMx) {
-          sfa_src = p.sfa + (static_cast<int64_t>(m_tile128) * p.k_blocks + tc.kb0) * p.sfa_stage_bytes;
-          sfb_src = p.sfb + (static_cast<int64_t>(tc.n_tile) * p.k_blocks + tc.kb0) * p.sfb_stage_bytes;
-          sfa_atom = (m_tile128 * p.k_blocks + tc.kb0) * sfa_atoms_ld;
-          sfb_atom = (tc.n_tile * p.k_blocks + tc.kb0) * sfb_atoms_ld;
+          sfa_base = p.sfa + static_cast<int64_t>(m_tile128) * p.k_blocks * p.sfa_stage_bytes;
+          sfb_base = p.sfb + static_cast<int64_t>(tc.n_tile) * p.k_blocks * p.sfb_stage_bytes;
         }
         for (int i = 0; i < tc.nkb; ++i, kx += 128) {
           if (!peek && !__all_sync(0xffffffffu, mbar_wait_bounded(empty_addr, ph ^ 1u, abort_flag))) {
@@ -288,7 +282,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                                                          (wrap ? (ph ^ 1u) : ph) ^ 1u)) ? 1u : 0u;
           }
           if (leader) {
-            mbar_expect_tx_p(full_bar(s), tx_total, el);
+            mbar_expect_tx_p(full_bar(s), tx_bytes * kCtas, el);
             armed |= 1u << s;
             armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
           }
@@ -305,17 +299,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               tma_load_2d_g<kPair>(b_dst + c * 16384, &tmB, full_addr, n0 + c * 128, kx, el);
           }
           if constexpr (kMx) {
+            const int kb = tc.kb0 + i;
             if constexpr (kPair) {
               // rows of 512 bytes (one atom each) of the re-laid-out scale arrays
-              tma_load_2d_g<true>(sf_dst, &tmSFA, full_addr, 0, sfa_atom, el);
-              tma_load_2d_g<true>(sf_dst + sfa_bytes, &tmSFB, full_addr, 0, sfb_atom, el);
-              sfa_atom += sfa_atoms_ld;
-              sfb_atom += sfb_atoms_ld;
+              tma_load_2d_g<true>(sf_dst, &tmSFA, full_addr, 0, (m_tile128 * p.k_blocks + kb) * sfa_atoms_ld, el);
+              tma_load_2d_g<true>(sf_dst + sfa_bytes, &tmSFB, full_addr, 0,
+                                  (tc.n_tile * p.k_blocks + kb) * sfb_atoms_ld, el);
             } else {
-              bulk_load_p(sf_dst, sfa_src, sfa_bytes, full_addr, el);
-              bulk_load_p(sf_dst + sfa_bytes, sfb_src, sfb_bytes, full_addr, el);
-              sfa_src += sfa_bytes;
-              sfb_src += sfb_bytes;
+              bulk_load_p(sf_dst, sfa_base + static_cast<int64_t>(kb) * sfa_bytes, sfa_bytes, full_addr, el);
+              bulk_load_p(sf_dst + sfa_bytes, sfb_base + static_cast<int64_t>(kb) * sfb_bytes, sfb_bytes, full_addr,
+                          el);
             }
           }
           if (++s == stages) {
@@ -384,16 +377,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         id3 = id1;
       }
       const uint32_t sf_t0 = tmem_base + sf_col0;
-      uint32_t sfa_t = sf_t0, sf_q = 0, sf_ph = 0, peek_sf = 0;
+      uint32_t sfa_t = sf_t0, sf_q = 0;
+      const uint32_t sf_hi = static_cast<uint32_t>(sf_hi64 >> 32);
+      const uint32_t sf_lo0 = static_cast<uint32_t>(sf_hi64) | (sf_base >> 4);
+      const uint32_t sf_step = static_cast<uint32_t>(sf_stage) >> 4;
       const uint32_t sfa_half = 4u, sfb_half = 2u * sfb_atoms;  // mxf4: second 4-block atom row
       const uint32_t full0 = full_bar(0), empty0 = empty_bar(0);
 
       const bool dbg = p.clk_dbg != nullptr && blockIdx.x == 0;
-      long long dbg_wait_acc = 0, dbg_wait_full = 0, dbg_wait_sf = 0;
+      long long dbg_wait_acc = 0, dbg_wait_full = 0;
       const long long dbg_start = dbg ? clock64() : 0;
       int s = 0, buf = 0;
       uint32_t ph = 0, acc_ph = 0, peek = 0;
-      uint32_t a_lo = a_lo0, b_lo = b_lo0, full_addr = full0, empty_addr = empty0;
+      uint32_t a_lo = a_lo0, b_lo = b_lo0, full_addr = full0, empty_addr = empty0, sf_lo = sf_lo0;
       for (int t = work0; t < total_tiles && ok; t += work_step) {
         const TileCoord tc = decode_tile(p, t);
         long long tw0 = dbg ? clock64() : 0;
@@ -419,20 +415,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           const uint32_t nph = (s + 1 == stages) ? (ph ^ 1u) : ph;
           peek = __all_sync(kAll, mbar_test_wait(nfull, nph)) ? 1u : 0u;
           const uint32_t sfb_t = sfa_t + 4u * sfa_atoms;
-          if constexpr (kMx) {
-            // the k-block's scale factors, copied into this slot by the scale copier
-            tw0 = dbg ? clock64() : 0;
-            if (!peek_sf && !__all_sync(kAll, mbar_wait_bounded(sf_full_bar(sf_q), sf_ph, abort_flag))) {
-              if (el) record_error(p, abort_flag, kErrMmaWaitFull);
-              ok = false;
-              break;
-            }
-            if (dbg) dbg_wait_sf += clock64() - tw0;
-            const bool wrap = sf_q + 1 == sf_slots;
-            peek_sf = __all_sync(kAll, mbar_test_wait(sf_full_bar(wrap ? 0u : sf_q + 1),
-                                                      wrap ? (sf_ph ^ 1u) : sf_ph)) ? 1u : 0u;
-          }
           tc_fence_after_sync();
+          if constexpr (kMx) {
+            // this k-block's scale atoms: shared -> the slot's tensor-memory columns
+            uint32_t src = sf_lo, dst = sfa_t;
+            for (uint32_t a = 0; a < sf_atoms; ++a, src += 32, dst += 4)
+              tmem_cp_atom_g<kPair>(dst, src, sf_hi, el);
+          }
           if constexpr (KIND == kKindI8) {
             mma_i8_g<kPair>(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc, accumulate, el);
             mma_i8_g<kPair>(d_tmem, a_lo + a_k, a_hi, b_lo + b_k, b_hi, idesc, 1u, el);
@@ -455,7 +444,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             sfa_t += sf_cols;
             if (++sf_q == sf_slots) {
               sf_q = 0;
-              sf_ph ^= 1u;
               sfa_t = sf_t0;
             }
           }
@@ -466,11 +454,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             b_lo = b_lo0;
             full_addr = full0;
             empty_addr = empty0;
+            sf_lo = sf_lo0;
           } else {
             a_lo += stage_step;
             b_lo += stage_step;
             full_addr += 8;
             empty_addr += 8;
+            sf_lo += sf_step;
           }
         }
         if (ok) tc_commit_both<kPair>(acc_full_bar(buf), el);
@@ -488,80 +478,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         p.clk_dbg[2] = static_cast<unsigned long long>(clock64() - dbg_start);
         p.clk_dbg[3] = static_cast<unsigned long long>(dbg_wait_full);
         p.clk_dbg[4] = static_cast<unsigned long long>(dbg_wait_acc);
-        p.clk_dbg[7] = static_cast<unsigned long long>(dbg_wait_sf);
-      }
-    }
-    __syncwarp();
-  } else if (warp == 6) {
-    // ------------------------------ scale copier ------------------------------
-    // MX only.  For every k-block: wait for its stage to land, wait until the MMAs that
-    // last read the target slot are done, copy the atoms shared -> tensor memory and let
-    // tcgen05.commit announce them on the slot's barrier.
-    if constexpr (kMx) {
-      if (leader) {
-        const uint32_t el = elect_one() ? 1u : 0u;
-        constexpr uint32_t kAll = 0xffffffffu;
-        const uint32_t sf_hi = static_cast<uint32_t>(sf_hi64 >> 32);
-        const uint32_t sf_lo0 = static_cast<uint32_t>(sf_hi64) | (sf_base >> 4);
-        const uint32_t sf_step = static_cast<uint32_t>(sf_stage) >> 4;
-        const uint32_t sf_t0 = tmem_base + sf_col0;
-        // With fewer slots than stages the slot's previous readers are the MMAs of the
-        // k-block `sf_slots` earlier: their commit is the empty barrier of that stage.
-        // With at least as many slots as stages the stage's own full barrier implies it.
-        const bool need_free = sf_slots < static_cast<uint32_t>(stages);
-        int s = 0, fs = 0;            // stage of this k-block / of the k-block sf_slots earlier
-        uint32_t ph = 0, fph = 0, q = 0, it = 0, peek_full = 0;
-        uint32_t sf_lo = sf_lo0, dst0 = sf_t0;
-        bool ok = true;
-        for (int t = work0; t < total_tiles && ok; t += work_step) {
-          const TileCoord tc = decode_tile(p, t);
-          for (int i = 0; i < tc.nkb; ++i, ++it) {
-            if (!peek_full && !__all_sync(kAll, mbar_wait_bounded(full_bar(s), ph, abort_flag))) {
-              if (el) record_error(p, abort_flag, kErrMmaWaitFull);
-              ok = false;
-              break;
-            }
-            if (need_free && it >= sf_slots) {
-              if (!__all_sync(kAll, mbar_wait_bounded(empty_bar(fs), fph, abort_flag))) {
-                if (el) record_error(p, abort_flag, kErrMmaWaitFull);
-                ok = false;
-                break;
-              }
-              if (++fs == stages) {
-                fs = 0;
-                fph ^= 1u;
-              }
-            }
-            {
-              const int ns = (s + 1 == stages) ? 0 : s + 1;
-              peek_full = __all_sync(kAll, mbar_test_wait(full_bar(ns), ns == 0 ? (ph ^ 1u) : ph)) ? 1u : 0u;
-            }
-            tc_fence_after_sync();
-            uint32_t src = sf_lo, dst = dst0;
-            const uint32_t n_cp = (p.debug_flags & 8) ? (sf_atoms > 1 ? 1u : 0u) : sf_atoms;  // experiments
-            for (uint32_t a = 0; a < n_cp; ++a, src += 32, dst += 4)
-              tmem_cp_atom_g<kPair>(dst, src, sf_hi, el);
-            tc_commit_g<kPair>(sf_full_bar(q), el);
-            if (++q == sf_slots) {
-              q = 0;
-              dst0 = sf_t0;
-            } else {
-              dst0 += sf_cols;
-            }
-            if (++s == stages) {
-              s = 0;
-              ph ^= 1u;
-              sf_lo = sf_lo0;
-            } else {
-              sf_lo += sf_step;
-            }
-          }
-        }
-        // no copy may be in flight when tensor memory is released
-        tc_commit_g<kPair>(sf_drain_bar, el);
-        int dummy = 0;
-        if (!__all_sync(kAll, mbar_wait_bounded(sf_drain_bar, 0, &dummy)) && el)
-          record_error(p, abort_flag, kErrDrainWait);
+        p.clk_dbg[7] = 0;
       }
     }
     __syncwarp();
