@@ -387,6 +387,7 @@ def main():
     barrier()
     if c.stream_status(stream) != c.Status.kSuccess:
         raise RuntimeError("device-side error during warm-up: " + _capi.last_error())
+    plan = _capi.last_plan()
     launches0 = c.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_wall0 = time.perf_counter()
@@ -474,7 +475,12 @@ def main():
             "metric": metric_name(wl), "value": value, "unit": unit, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
-            "data": "synthetic", "config": config_of(wl, world), "clocks": clocks,
+            "data": "synthetic",
+            "config": dict(config_of(wl, world), kernel_plan={
+                "tile": f"{256 if plan.pair else 128}x{plan.tile_n}", "cta_pair": bool(plan.pair),
+                "operands_swapped": bool(plan.swapped), "k_slices": plan.slices,
+                "smem_stages": plan.stages, "ctas": plan.grid}),
+            "clocks": clocks,
             "gpu_launches": int(launches), "roofline": roofline, "impl": "b200",
         }
         if e2e:
