@@ -296,6 +296,42 @@ int make_tensor_map_words(CUtensorMap* tm, const void* base, uint64_t cols, uint
   return 0;
 }
 
+// Packed 4-bit rows (k elements, two per byte) read as 128-element boxes that land in
+// shared memory in the padded form kind::mxf8f6f4 takes: 16 elements per 16 bytes, so a
+// box row is 128 bytes and the 128-byte swizzle applies as for 8-bit operands.  The
+// driver requires a 32-byte aligned base and pitch and an inner extent that is a
+// multiple of 128 elements: the extent is rounded up, and the caller guarantees that
+// the rounded row still lies inside the pitch.
+int make_tensor_map_fp4_padded(CUtensorMap* tm, const void* base, uint64_t k_elems, uint64_t outer,
+                               uint64_t pitch, uint32_t box_outer) {
+  const uint64_t k128 = (k_elems + 127) / 128 * 128;
+  if (outer <= 1) pitch = k128 / 2;
+  const TensorMapKey key{reinterpret_cast<uint64_t>(base), k128, outer, pitch, box_outer, 3u};
+  TensorMapSlot& slot = tensor_map_slot(key);
+  if (slot.valid && slot.key == key) {
+    *tm = slot.map;
+    return 0;
+  }
+  const cuuint64_t dims[2] = {k128, outer};
+  const cuuint64_t strides[1] = {pitch};
+  const cuuint32_t box[2] = {128, box_outer};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r =
+      g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, const_cast<void*>(base), dims, strides,
+               box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled (padded fp4) failed with %d (base %p k %llu outer %llu pitch %llu)",
+              static_cast<int>(r), base, (unsigned long long)k128, (unsigned long long)outer,
+              (unsigned long long)pitch);
+    return CPUOPS_B200_STATUS_CUDA_ERROR;
+  }
+  slot.valid = true;
+  slot.key = key;
+  slot.map = *tm;
+  return 0;
+}
+
 // The re-laid-out scale array as rows of one 512-byte atom each (128 words, not
 // swizzled); a box is the `box_atoms` atoms of one k-block.
 int make_tensor_map_atoms(CUtensorMap* tm, const void* base, uint64_t n_atoms, uint32_t box_atoms) {
@@ -606,10 +642,11 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     // (gemm.h:106-110); C and D themselves are dereferenced, so they must exist.
     if (!d->c || !d->d) return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
   }
-  if (is_mx && (fp4_a != fp4_b)) {
-    set_error("mixing fp4 with fp8 operands is not built yet");
-    return CPUOPS_B200_STATUS_UNSUPPORTED;
-  }
+  // fp4 x fp8 (GemmMx<SA, SB> allows any pair, gemm_mx.h:44-47): both operands go through
+  // kind::mxf8f6f4, whose 4-bit operand sits in shared memory as 16 elements per 16 bytes
+  // (8 data + 8 padding); TMA produces that form from the packed bytes (tensor-map type
+  // 16U4_ALIGN16B), so a k-block is 128 elements for both operands.
+  const bool mixed = is_mx && (fp4_a != fp4_b);
   for (int t = 0; t < d->n_ops; ++t) {
     const int oc = d->ops[t].opcode;
     if (oc < CPUOPS_B200_OP_RELU || oc > CPUOPS_B200_OP_SILU) {
@@ -666,9 +703,10 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
 
   // ---- configuration -----------------------------------------------------------------
   Choice ch;
-  const int elems_per_block = (fp4_a ? 256 : 128);  // k elements per 128-byte stage row
+  const bool fp4_pair = fp4_a && fp4_b;
+  const int elems_per_block = (fp4_pair ? 256 : 128);  // k elements per 128-byte stage row
   const int k_blocks = k > 0 ? (k + elems_per_block - 1) / elems_per_block : 0;
-  const int kind = !is_mx ? kKindI8 : (fp4_a ? kKindMxf4 : kKindMxf8);
+  const int kind = !is_mx ? kKindI8 : (fp4_pair ? kKindMxf4 : kKindMxf8);
   if (k > 0) {
     ch.swap = (m <= 64 && n > m);
     const int Mk = ch.swap ? n : m, Nk = ch.swap ? m : n;
@@ -822,20 +860,26 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
   bool a_repack = false, b_repack = false;
   const bool a_mask = fp4_a && (k & 1), b_mask = fp4_b && (k & 1);
   if (k > 0) {
+    // The padded 4-bit tensor map wants a 32-byte aligned base and pitch and whole
+    // 128-element (64-byte) boxes inside every row's pitch.
+    const bool a_pad = mixed && fp4_a, b_pad = mixed && fp4_b;
+    auto pad_ok = [&](const void* base, int64_t pitch) {
+      return (reinterpret_cast<uintptr_t>(base) & 31u) == 0 && (pitch & 31) == 0 && (k & 127) == 0;
+    };
     if (!a_dev) {
-      a_pitch_dev = align_up(A.inner_bytes, 16);
+      a_pitch_dev = align_up(A.inner_bytes, a_pad ? 64 : 16);
       off_a = plan.take(a_pitch_dev * A.outer);
-    } else if (!tma_addressable(d->a, A.pitch, A.outer) || a_mask) {
+    } else if (!tma_addressable(d->a, A.pitch, A.outer) || a_mask || (a_pad && !pad_ok(d->a, A.pitch))) {
       a_repack = true;
-      a_pitch_dev = align_up(A.inner_bytes, 16);
+      a_pitch_dev = align_up(A.inner_bytes, a_pad ? 64 : 16);
       off_a = plan.take(a_pitch_dev * A.outer);
     }
     if (!b_dev) {
-      b_pitch_dev = align_up(B.inner_bytes, 16);
+      b_pitch_dev = align_up(B.inner_bytes, b_pad ? 64 : 16);
       off_b = plan.take(b_pitch_dev * B.outer);
-    } else if (!tma_addressable(d->b, B.pitch, B.outer) || b_mask) {
+    } else if (!tma_addressable(d->b, B.pitch, B.outer) || b_mask || (b_pad && !pad_ok(d->b, B.pitch))) {
       b_repack = true;
-      b_pitch_dev = align_up(B.inner_bytes, 16);
+      b_pitch_dev = align_up(B.inner_bytes, b_pad ? 64 : 16);
       off_b = plan.take(b_pitch_dev * B.outer);
     }
     if (is_mx) {
@@ -866,7 +910,7 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     Mk = ch.swap ? n : m;
     Nk = ch.swap ? m : n;
     if (is_mx) {
-      bps = fp4_a ? 8 : 4;
+      bps = fp4_pair ? 8 : 4;
       // a pair always reads the scales of both of its 128-row halves
       sfa_bytes = cpuops_b200_scale_layout_bytes(ch.pair ? static_cast<int>(align_up(Mk, 256)) : Mk, k,
                                                  kTileM, bps);
@@ -1026,11 +1070,22 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
 
     // ---- tensor maps -----------------------------------------------------------------------
     CUtensorMap tmA, tmB;
-    if (int rc = make_tensor_map(&tmA, ak_ptr, AkM.inner_bytes, AkM.outer, ak_pitch, 128)) return rc;
+    const bool ak_pad = mixed && (swap ? fp4_b : fp4_a), bk_pad = mixed && (swap ? fp4_a : fp4_b);
     const int b_rows = ch.pair ? ch.BN / 2 : ch.BN;  // rows of the B tile staged per CTA
-    if (int rc = make_tensor_map(&tmB, bk_ptr, BkM.inner_bytes, BkM.outer, bk_pitch,
-                                 bk_kmajor ? static_cast<uint32_t>(b_rows) : 128u))
-      return rc;
+    if (ak_pad) {
+      if (int rc = make_tensor_map_fp4_padded(&tmA, ak_ptr, k, AkM.outer, ak_pitch, 128)) return rc;
+    } else {
+      if (int rc = make_tensor_map(&tmA, ak_ptr, AkM.inner_bytes, AkM.outer, ak_pitch, 128)) return rc;
+    }
+    if (bk_pad) {
+      if (int rc = make_tensor_map_fp4_padded(&tmB, bk_ptr, k, BkM.outer, bk_pitch,
+                                              static_cast<uint32_t>(b_rows)))
+        return rc;
+    } else {
+      if (int rc = make_tensor_map(&tmB, bk_ptr, BkM.inner_bytes, BkM.outer, bk_pitch,
+                                   bk_kmajor ? static_cast<uint32_t>(b_rows) : 128u))
+        return rc;
+    }
 
     GemmParams p;
     memset(&p, 0, sizeof(p));
@@ -1044,6 +1099,7 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     p.slices = ch.slices;
     p.BN = ch.BN;
     p.nacc = ch.nacc;
+    p.tx_operand_bytes = kTileM * (ak_pad ? 64 : 128) + b_rows * (bk_pad ? 64 : 128);
     {
       // One wave of CTAs covers g m-tiles x (SMs / g) n-tiles; its L2 footprint per
       // k-block, g * 128 + (SMs / g) * BN rows, is smallest for g = sqrt(SMs * BN / 128).
@@ -1059,8 +1115,9 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
       p.idesc = make_idesc(2 /*s32*/, a_fmt, b_fmt, p.a_mn_major, p.b_mn_major, tile_m, ch.BN);
     } else if (kind == kKindMxf8) {
       const int fa = swap ? d->b_format : d->a_format, fb = swap ? d->a_format : d->b_format;
-      p.idesc = make_idesc_block_scaled(fa == CPUOPS_B200_FMT_E5M2 ? 1u : 0u,
-                                        fb == CPUOPS_B200_FMT_E5M2 ? 1u : 0u, tile_m, ch.BN);
+      // kind::mxf8f6f4 format codes: E4M3 0, E5M2 1, E2M1 5
+      auto code = [](int f) { return f == CPUOPS_B200_FMT_E5M2 ? 1u : (f == CPUOPS_B200_FMT_E2M1 ? 5u : 0u); };
+      p.idesc = make_idesc_block_scaled(code(fa), code(fb), tile_m, ch.BN);
     } else {
       p.idesc = make_idesc_block_scaled(1u, 1u, tile_m, ch.BN);  // e2m1 x e2m1
     }
@@ -1445,6 +1502,7 @@ CPUOPS_B200_API int cpuops_b200_gemm_i8_noalloc(const cpuops_b200_gemm_desc* d) 
   p.BN = BN;
   p.nacc = 2;
   p.raster_m = 8;
+  p.tx_operand_bytes = gemm_stage_bytes(p.BN);
   p.a_mn_major = a_kmajor ? 0 : 1;
   p.b_mn_major = b_kmajor ? 0 : 1;
   p.idesc = make_idesc(2 /*s32*/, 0u /*u8*/, 1u /*s8*/, p.a_mn_major, p.b_mn_major, kTileM, BN);

@@ -246,7 +246,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       int s = 0;
       uint32_t ph = 0, armed = 0, armed_parity = 0, peek = 0;
       bool ok = true;
-      const uint32_t tx_bytes = static_cast<uint32_t>(stage_bytes + sf_stage);
+      // (a packed 4-bit operand of a mixed-format GEMM credits only its 64 data bytes per
+      // 128-byte shared-memory row, so the count comes from the launcher)
+      const uint32_t tx_bytes = static_cast<uint32_t>(p.tx_operand_bytes + sf_stage);
       // pair: every load of both CTAs credits the leader's barrier, which alone is armed
       // (by the leader's producer) with the bytes of both
       const uint32_t full0 = kPair ? map_to_cta(full_bar(0), 0) : full_bar(0), empty0 = empty_bar(0);

@@ -75,6 +75,7 @@ struct GemmParams {
   const uint8_t* sfb;
   int32_t sfa_stage_bytes, sfb_stage_bytes;  // per k-block
   int32_t c_ring;           // 1: C tiles are prefetched by TMA into a shared-memory ring
+  int32_t tx_operand_bytes; // bytes the A and B loads of one stage credit to the barrier, per CTA
   int32_t* error;           // device error word
   int32_t debug_flags;      // experiments only (CPUOPS_B200_DEBUG)
   unsigned long long* clk_dbg;  // experiments only: {SM cycles, nanoseconds} of CTA 0
