@@ -198,6 +198,7 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 // Experiment switches, read from the environment once.
 struct EnvSwitches {
   bool no_c_ring = getenv("CPUOPS_B200_NO_C_RING") != nullptr;
+  bool no_d_tma = getenv("CPUOPS_B200_NO_D_TMA") != nullptr;
   bool clk = getenv("CPUOPS_B200_CLK") != nullptr;
   int debug_flags = getenv("CPUOPS_B200_DEBUG") ? atoi(getenv("CPUOPS_B200_DEBUG")) : 0;
   int raster_m = getenv("CPUOPS_B200_RASTER") ? atoi(getenv("CPUOPS_B200_RASTER")) : 0;
@@ -1154,6 +1155,14 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
       if (int rc = make_tensor_map_words(&tmC, epi.C, Nk, Mk, epi.c_sr * 4)) return rc;
       p.c_ring = 1;
     }
+    // D through the same ring by TMA store when it is row-contiguous and addressable.
+    CUtensorMap tmD = tmA;
+    if (p.mode == kModeEpilogue && epi.d_sc == 1 && tma_addressable(epi.D, epi.d_sr * 4, Mk) &&
+        !env_switches().no_d_tma) {
+      if (int rc = make_tensor_map_words(&tmD, epi.D, Nk, Mk, epi.d_sr * 4)) return rc;
+      p.d_tma = 1;
+    }
+    p.ring_bufs = (p.c_ring || p.d_tma) ? 2 : 0;
     p.error = st.error_dev;
     p.debug_flags = env_switches().debug_flags;
     if (env_switches().clk) {
@@ -1164,7 +1173,8 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     }
     const int sf_stage_bytes = p.sfa_stage_bytes + p.sfb_stage_bytes;
     const int per_stage = gemm_stage_bytes(b_rows) + sf_stage_bytes;
-    int stages = (st.smem_optin - 1024 - kBarrierBytes - (p.c_ring ? 1024 + kCRingBytes : 0)) / per_stage;
+    int stages = (st.smem_optin - 1024 - kBarrierBytes - (p.ring_bufs ? 1024 + ring_bytes(p.ring_bufs) : 0)) /
+                 per_stage;
     stages = std::min({stages, kMaxStages, std::max(2, k_blocks)});
     if (stages < 2) {
       set_error("internal: shared memory too small for two stages");
@@ -1172,7 +1182,7 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     }
     p.stages = stages;
     // At least 120 KB so that two CTAs never share an SM: each allocates all of tensor memory.
-    const int smem = std::max(gemm_smem_bytes(b_rows, stages, sf_stage_bytes, p.c_ring),
+    const int smem = std::max(gemm_smem_bytes(b_rows, stages, sf_stage_bytes, p.ring_bufs),
                               120 * 1024);
     const int64_t total_tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles * p.slices;
     unsigned grid = static_cast<unsigned>(std::min<int64_t>(total_tiles, st.sm_count));
@@ -1248,21 +1258,21 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     cfg.numAttrs = n_attr;
     if (kind == kKindI8) {
       if (ch.pair) {
-        CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<kKindI8, true>, tmA, tmB, tmC, tmSFA, tmSFB, p));
+        CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<kKindI8, true>, tmA, tmB, tmC, tmD, tmSFA, tmSFB, p));
       } else {
-        CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<kKindI8, false>, tmA, tmB, tmC, tmSFA, tmSFB, p));
+        CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<kKindI8, false>, tmA, tmB, tmC, tmD, tmSFA, tmSFB, p));
       }
     } else if (kind == kKindMxf8) {
       if (ch.pair) {
-        CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<kKindMxf8, true>, tmA, tmB, tmC, tmSFA, tmSFB, p));
+        CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<kKindMxf8, true>, tmA, tmB, tmC, tmD, tmSFA, tmSFB, p));
       } else {
-        CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<kKindMxf8, false>, tmA, tmB, tmC, tmSFA, tmSFB, p));
+        CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<kKindMxf8, false>, tmA, tmB, tmC, tmD, tmSFA, tmSFB, p));
       }
     } else {
       if (ch.pair) {
-        CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<kKindMxf4, true>, tmA, tmB, tmC, tmSFA, tmSFB, p));
+        CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<kKindMxf4, true>, tmA, tmB, tmC, tmD, tmSFA, tmSFB, p));
       } else {
-        CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<kKindMxf4, false>, tmA, tmB, tmC, tmSFA, tmSFB, p));
+        CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<kKindMxf4, false>, tmA, tmB, tmC, tmD, tmSFA, tmSFB, p));
       }
     }
     g_launches.fetch_add(1);
@@ -1524,7 +1534,7 @@ CPUOPS_B200_API int cpuops_b200_gemm_i8_noalloc(const cpuops_b200_gemm_desc* d) 
   const int smem = std::max(gemm_smem_bytes(BN, stages, 0), 120 * 1024);
   const int64_t total_tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles * p.slices;
   const unsigned grid = static_cast<unsigned>(std::min<int64_t>(total_tiles, nd->sm_count));
-  gemm_tcgen05_kernel<kKindI8, false><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, tmA /*unused: no C ring*/,
+  gemm_tcgen05_kernel<kKindI8, false><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, tmA, tmA /*unused: no ring*/,
                                                                             tmA, tmA /*unused: MX pair only*/, p);
   g_launches.fetch_add(1);
   CUDA_TRY(cudaGetLastError());

@@ -72,10 +72,12 @@ __device__ __forceinline__ bool aligned16(const void* ptr) {
 }
 
 // Stores one 32-column chunk of one accumulator row.
+// `c_smem_row`: this thread's row of the C chunk prefetched into the ring, or null.
+// `d_smem_row`: where to put the finished row for the TMA store, or null (store directly).
 template <bool kInt>
 __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[32], int krow,
                                             int kcol0, int slice, const uint32_t* c_smem_row,
-                                            int c_swz) {
+                                            uint32_t* d_smem_row, int c_swz) {
   const int ncols = min(32, p.Nk - kcol0);
   if (p.mode == kModePartial) {
     uint32_t* w = static_cast<uint32_t*>(p.ws) + (slice * p.ws_slab + krow * p.ws_sr + kcol0 * p.ws_sc);
@@ -119,6 +121,14 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[3
 #pragma unroll
   for (int i = 0; i < 32; ++i) r[i] = linear_combine_bits<kInt>(e, r[i], src[i]);
   for (int t = 0; t < e.n_ops; ++t) apply_op_chunk<kInt>(e.ops[t], r, krow, kcol0, ncols);
+  if (d_smem_row != nullptr) {
+    // same 16-byte-piece swizzle as the TMA box (row & 7)
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      *reinterpret_cast<uint4*>(d_smem_row + ((j ^ c_swz) << 2)) =
+          make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+    return;
+  }
   uint32_t* d = static_cast<uint32_t*>(e.D) + (krow * e.d_sr + kcol0 * e.d_sc);
   if (e.d_sc == 1 && ncols == 32 && aligned16(d)) {
 #pragma unroll
@@ -142,6 +152,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                         const __grid_constant__ CUtensorMap tmB,
                         const __grid_constant__ CUtensorMap tmC,
+                        const __grid_constant__ CUtensorMap tmD,
                         const __grid_constant__ CUtensorMap tmSFA,
                         const __grid_constant__ CUtensorMap tmSFB, const GemmParams p) {
   constexpr bool kInt = (KIND == kKindI8);
@@ -168,7 +179,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const uint32_t sf_base = smem_base + stages * stage_bytes;
   // Optional ring of C chunks (32 rows x 32 columns, 128-byte swizzled), two per epilogue warp.
   const uint32_t c_base = (sf_base + stages * sf_stage + 1023u) & ~1023u;
-  const uint32_t bar_base = p.c_ring ? c_base + kCRingBytes : sf_base + stages * sf_stage;
+  const uint32_t bar_base = p.ring_bufs ? c_base + ring_bytes(p.ring_bufs) : sf_base + stages * sf_stage;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
   auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * kMaxStages + b); };
@@ -489,18 +500,31 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const int q = warp & 3;  // the TMEM lane quarter this warp can read
     int it = 0;
     const int nchunks = p.BN / 32;
-    // C ring: two 4 KB buffers per warp, filled by TMA two chunks ahead of their use.
-    const bool ring = p.c_ring != 0;
-    const uint32_t my_c = c_base + static_cast<uint32_t>(q) * 8192u;
-    const uint8_t* my_c_ptr = smem + (my_c - smem_base);
-    uint32_t cq = 0;  // chunks consumed so far by this warp (selects buffer and parity)
-    uint32_t cissued = 0;
+    // Ring of two 4 KB chunk buffers per warp (32 rows x 32 words, 128-byte swizzled);
+    // chunk x uses buffer x % 2.  With c_ring, C chunks are fetched into it by TMA two
+    // chunks ahead of their use; with d_tma, the finished chunk is written into its
+    // buffer (in place over C) and leaves by TMA store, so D is written in whole 128-byte
+    // row pieces; a buffer is refilled only after the store that read it is done with it.
+    // (A third buffer would hide that wait but costs a pipeline stage: measured slower.)
+    const bool ring = p.c_ring != 0, d_tma = p.d_tma != 0;
+    const uint32_t nb = static_cast<uint32_t>(p.ring_bufs);
+    const uint32_t my_c = c_base + static_cast<uint32_t>(q) * nb * 4096u;
+    uint8_t* my_c_ptr = smem + (my_c - smem_base);
+    uint32_t cq = 0;        // chunks consumed so far by this warp
+    uint32_t cq_b = 0, cq_ph = 0;  // its buffer and that buffer's barrier parity
+    uint32_t cissued = 0, ci_b = 0;  // C chunks requested so far, buffer of the next request
     bool alive = true;
     const bool edbg = p.clk_dbg != nullptr && blockIdx.x == 0 && warp == 2 && lane == 0;
     long long edbg_wait = 0;
     const long long edbg_start = edbg ? clock64() : 0;
     // pair: the leader's MMA thread waits for the epilogue warps of both CTAs
     const uint32_t acc_empty0 = kPair ? map_to_cta(acc_empty_bar(0), 0) : acc_empty_bar(0);
+    auto request_c = [&](int col, int row) {  // lane 0 only
+      mbar_expect_tx(c_full_bar(q, ci_b), 4096u);
+      tma_load_2d(my_c + ci_b * 4096u, &tmC, c_full_bar(q, ci_b), col, row);
+      ++cissued;
+      if (++ci_b == nb) ci_b = 0;
+    };
     for (int t = work0; t < total_tiles && alive; t += work_step, ++it) {
       const TileCoord tc = decode_tile(p, t);
       const int buf = it % nacc;
@@ -510,11 +534,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const int n0 = tc.n_tile * p.BN;
       if (ring && lane == 0) {
         // first two chunks of this tile: requested before the accumulator is ready
-        for (int c = 0; c < 2 && c < nchunks; ++c, ++cissued) {
-          const uint32_t b = cissued & 1u;
-          mbar_expect_tx(c_full_bar(q, b), 4096u);
-          tma_load_2d(my_c + b * 4096u, &tmC, c_full_bar(q, b), n0 + c * 32, row0);
-        }
+        if (d_tma) bulk_wait_group_read<0>();
+        for (int c = 0; c < 2 && c < nchunks; ++c) request_c(n0 + c * 32, row0);
       }
       const long long te0 = edbg ? clock64() : 0;
       const bool ready = mbar_wait_bounded(acc_full_bar(buf), acc_ph, abort_flag);
@@ -545,30 +566,47 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
         const int kcol0 = n0 + c * 32;
         const uint32_t* c_row = nullptr;
+        uint32_t* d_row = nullptr;
         if (ring) {
-          const uint32_t b = cq & 1u;
-          const bool got = mbar_wait_bounded(c_full_bar(q, b), (cq >> 1) & 1u, abort_flag);
+          const bool got = mbar_wait_bounded(c_full_bar(q, cq_b), cq_ph, abort_flag);
           if (!__all_sync(0xffffffffu, got)) {
             if (lane == 0) record_error(p, abort_flag, kErrEpilogueWait);
             alive = false;
             break;
           }
-          c_row = reinterpret_cast<const uint32_t*>(my_c_ptr + b * 4096u + lane * 128);
+          c_row = reinterpret_cast<const uint32_t*>(my_c_ptr + cq_b * 4096u + lane * 128);
+        } else if (d_tma) {
+          // the store that last read this buffer (two chunks ago) must be done with it
+          if (lane == 0) bulk_wait_group_read<1>();
+          __syncwarp();
         }
+        if (d_tma) d_row = reinterpret_cast<uint32_t*>(my_c_ptr + cq_b * 4096u + lane * 128);
         if (krow < p.Mk && kcol0 < p.Nk && !(p.debug_flags & 4))
-          store_chunk<kInt>(p, r, krow, kcol0, tc.slice, c_row, lane & 7);
-        if (ring) {
-          ++cq;
-          __syncwarp();  // every lane has read its row: the buffer may be refilled
-          if (lane == 0 && c + 2 < nchunks) {
-            const uint32_t b = cissued & 1u;
-            mbar_expect_tx(c_full_bar(q, b), 4096u);
-            tma_load_2d(my_c + b * 4096u, &tmC, c_full_bar(q, b), n0 + (c + 2) * 32, row0);
-            ++cissued;
+          store_chunk<kInt>(p, r, krow, kcol0, tc.slice, c_row, d_row, lane & 7);
+        if (d_tma) {
+          fence_proxy_async_shared_cta();  // this lane's row -> visible to the TMA store
+          __syncwarp();
+          if (lane == 0) {
+            if (row0 < p.Mk && kcol0 < p.Nk) tma_store_2d(&tmD, my_c + cq_b * 4096u, kcol0, row0);
+            bulk_commit_group();
           }
+        } else if (ring) {
+          __syncwarp();  // every lane has read its row: the buffer may be refilled
+        }
+        if (ring && lane == 0 && c + 2 < nchunks) {
+          // chunk c + 2 goes where chunk c - 1 (three buffers) or chunk c (two) was
+          // chunk c + 2 reuses chunk c's buffer: its store must have read it first
+          if (d_tma) bulk_wait_group_read<0>();
+          request_c(n0 + (c + 2) * 32, row0);
+        }
+        ++cq;
+        if (++cq_b == nb) {
+          cq_b = 0;
+          cq_ph ^= 1u;
         }
       }
     }
+    if (d_tma && lane == 0) bulk_wait_group_all();  // D is complete before the kernel ends
     if (edbg) {
       p.clk_dbg[5] = static_cast<unsigned long long>(clock64() - edbg_start);
       p.clk_dbg[6] = static_cast<unsigned long long>(edbg_wait);
@@ -576,7 +614,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     if (ring && *abort_flag != 0 && lane == 0) {
       // let C chunks that were requested but never consumed land before the CTA exits
       int dummy = 0;
-      for (; cq < cissued; ++cq) mbar_wait_bounded(c_full_bar(q, cq & 1u), (cq >> 1) & 1u, &dummy);
+      for (; cq < cissued; ++cq) {
+        mbar_wait_bounded(c_full_bar(q, cq_b), cq_ph, &dummy);
+        if (++cq_b == nb) {
+          cq_b = 0;
+          cq_ph ^= 1u;
+        }
+      }
     }
   }
 

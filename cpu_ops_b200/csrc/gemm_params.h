@@ -75,6 +75,8 @@ struct GemmParams {
   const uint8_t* sfb;
   int32_t sfa_stage_bytes, sfb_stage_bytes;  // per k-block
   int32_t c_ring;           // 1: C tiles are prefetched by TMA into a shared-memory ring
+  int32_t d_tma;            // 1: D chunks leave through that ring by TMA store
+  int32_t ring_bufs;        // ring buffers per epilogue warp: 0 (no ring) or 2
   int32_t tx_operand_bytes; // bytes the A and B loads of one stage credit to the barrier, per CTA
   int32_t* error;           // device error word
   int32_t debug_flags;      // experiments only (CPUOPS_B200_DEBUG)
@@ -83,11 +85,12 @@ struct GemmParams {
 
 // Shared-memory footprint of one launch of the GEMM kernel.
 __host__ __device__ inline int gemm_stage_bytes(int BN) { return kTileM * 128 + BN * 128; }
-constexpr int kCRingBytes = 4 /*epilogue warps*/ * 2 /*buffers*/ * 4096;  // 32 rows x 32 cols x 4 B each
+// Epilogue ring: per epilogue warp `bufs` buffers of one 32 x 32-word chunk (4 KB).
+__host__ __device__ inline int ring_bytes(int bufs) { return 4 /*epilogue warps*/ * bufs * 4096; }
 constexpr int kBarrierBytes = 512;  // barriers, TMEM slot, abort flag
-__host__ __device__ inline int gemm_smem_bytes(int BN, int stages, int sf_stage_bytes, int c_ring = 0) {
+__host__ __device__ inline int gemm_smem_bytes(int BN, int stages, int sf_stage_bytes, int ring_bufs = 0) {
   return 1024 /*alignment slack*/ + stages * (gemm_stage_bytes(BN) + sf_stage_bytes) +
-         (c_ring ? 1024 + kCRingBytes : 0) + kBarrierBytes;
+         (ring_bufs ? 1024 + ring_bytes(ring_bufs) : 0) + kBarrierBytes;
 }
 
 }  // namespace b200

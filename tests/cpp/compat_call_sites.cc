@@ -130,32 +130,32 @@ float decode_elem(const uint8_t* base, int row, int k, int ld) {
   }
 }
 
-template <typename T, typename LC>
+template <typename TA, typename TB, typename LC>
 void mx_case(int m, int n, int k, float alpha, float beta, int split_k_slices = 0) {
   ++g_cases;
-  const bool is_fp4 = std::is_same<T, fp4e2m1_t>::value;
-  const int ld = (k + 3) & ~(is_fp4 ? 1 : 0);
+  const bool a_fp4 = std::is_same<TA, fp4e2m1_t>::value, b_fp4 = std::is_same<TB, fp4e2m1_t>::value;
+  const int ld = (k + 3) & ~((a_fp4 || b_fp4) ? 1 : 0);
   const int ldc = (LC::kIsRowMajor ? n : m) + 3;
   const int kg = (k + 31) / 32, lds = kg + 1;
-  std::vector<uint8_t> A(static_cast<size_t>(m) * (ld / (is_fp4 ? 2 : 1)), 0);
-  std::vector<uint8_t> B(static_cast<size_t>(n) * (ld / (is_fp4 ? 2 : 1)), 0);
+  std::vector<uint8_t> A(static_cast<size_t>(m) * (ld / (a_fp4 ? 2 : 1)), 0);
+  std::vector<uint8_t> B(static_cast<size_t>(n) * (ld / (b_fp4 ? 2 : 1)), 0);
   std::vector<uint8_t> SA(static_cast<size_t>(m) * lds), SB(static_cast<size_t>(n) * lds);
   const size_t size_c = static_cast<size_t>(LC::kIsRowMajor ? m : n) * ldc;
   std::vector<float> C(size_c), D(size_c, std::numeric_limits<float>::quiet_NaN());
   std::mt19937 rng(static_cast<unsigned>(m * 131 + n * 17 + k));
-  auto fill = [&](std::vector<uint8_t>& data, std::vector<uint8_t>& scales) {
+  auto fill = [&](std::vector<uint8_t>& data, std::vector<uint8_t>& scales, bool e4m3, bool e5m2) {
     for (auto& b : data) {
       b = static_cast<uint8_t>(rng() & 0xFF);
-      if (std::is_same<T, fp8e4m3_t>::value && (b & 0x7F) == 0x7F) b &= 0xF7;
-      if (std::is_same<T, fp8e5m2_t>::value && (b & 0x7C) == 0x7C) b &= 0xBF;
+      if (e4m3 && (b & 0x7F) == 0x7F) b &= 0xF7;
+      if (e5m2 && (b & 0x7C) == 0x7C) b &= 0xBF;
     }
     for (auto& s : scales) s = static_cast<uint8_t>(124 + rng() % 7);
   };
-  fill(A, SA);
-  fill(B, SB);
+  fill(A, SA, std::is_same<TA, fp8e4m3_t>::value, std::is_same<TA, fp8e5m2_t>::value);
+  fill(B, SB, std::is_same<TB, fp8e4m3_t>::value, std::is_same<TB, fp8e5m2_t>::value);
   for (auto& x : C) x = static_cast<float>(static_cast<int>(rng() % 2001) - 1000) * 0.001f;
 
-  using Op = cpu_ops::gemm::device::GemmMx<T, T, LC>;
+  using Op = cpu_ops::gemm::device::GemmMx<TA, TB, LC>;
   typename Op::Arguments args;
   args.problem_size = {m, n, k};
   args.ref_A = {A.data(), SA.data(), ld, lds};
@@ -172,9 +172,9 @@ void mx_case(int m, int n, int k, float alpha, float beta, int split_k_slices = 
     for (int j = 0; j < n; ++j) {
       double acc = 0.0, bnd = 0.0;
       for (int p = 0; p < k; ++p) {
-        const double a = double(decode_elem<T>(A.data(), i, p, ld)) *
+        const double a = double(decode_elem<TA>(A.data(), i, p, ld)) *
                          cpu_ops::e8m0_to_float(SA[size_t(i) * lds + (p >> 5)]);
-        const double b = double(decode_elem<T>(B.data(), j, p, ld)) *
+        const double b = double(decode_elem<TB>(B.data(), j, p, ld)) *
                          cpu_ops::e8m0_to_float(SB[size_t(j) * lds + (p >> 5)]);
         acc += a * b;
         bnd += std::fabs(a * b);
@@ -262,12 +262,16 @@ int main(int argc, char** argv) {
     int8_case<RowMajor, RowMajor, RowMajor>(16, 24, 0, 1, 5, false);
     int8_case<RowMajor, RowMajor, RowMajor>(32, 32, 8192, 1, 1, true);
     int8_fused_case(96, 160, 700);
-    mx_case<fp8e4m3_t, RowMajor>(65, 63, 67, 1.0f, 0.0f);
-    mx_case<fp8e4m3_t, ColumnMajor>(31, 17, 258, 2.0f, -0.5f);
-    mx_case<fp8e5m2_t, RowMajor>(16, 6, 33, 1.0f, 0.25f);
-    mx_case<fp4e2m1_t, RowMajor>(128, 256, 96, 1.0f, 0.0f);
-    mx_case<fp4e2m1_t, ColumnMajor>(31, 17, 258, 0.5f, -0.5f);
-    mx_case<fp8e4m3_t, RowMajor>(24, 40, 3000, 1.25f, 0.5f, 7);
+    mx_case<fp8e4m3_t, fp8e4m3_t, RowMajor>(65, 63, 67, 1.0f, 0.0f);
+    mx_case<fp8e4m3_t, fp8e4m3_t, ColumnMajor>(31, 17, 258, 2.0f, -0.5f);
+    mx_case<fp8e5m2_t, fp8e5m2_t, RowMajor>(16, 6, 33, 1.0f, 0.25f);
+    mx_case<fp4e2m1_t, fp4e2m1_t, RowMajor>(128, 256, 96, 1.0f, 0.0f);
+    mx_case<fp4e2m1_t, fp4e2m1_t, ColumnMajor>(31, 17, 258, 0.5f, -0.5f);
+    mx_case<fp8e4m3_t, fp8e4m3_t, RowMajor>(24, 40, 3000, 1.25f, 0.5f, 7);
+    // any storage pair (gemm_mx.h:44-47)
+    mx_case<fp8e4m3_t, fp8e5m2_t, RowMajor>(33, 47, 77, 1.0f, 0.5f);
+    mx_case<fp8e4m3_t, fp4e2m1_t, RowMajor>(65, 63, 131, 1.0f, 0.0f);
+    mx_case<fp4e2m1_t, fp8e5m2_t, ColumnMajor>(40, 24, 256, 0.5f, 0.25f);
   } else {
     std::printf("usage: compat_call_sites --status | --gpu | --codecs in out\n");
     return 2;
