@@ -327,6 +327,12 @@ def main():
     ap.add_argument("--tile-n", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--graph", action="store_true",
+                    help="replay the calls from a CUDA graph (one trip round the operand ring per "
+                         "replay), as a launch-bound decode loop would; steps are rounded to whole trips")
+    ap.add_argument("--prepared-b", action="store_true",
+                    help="MX workloads: register each B operand once (cpuops_b200_prepare_b), as a "
+                         "decode loop with fixed weights would")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -369,11 +375,42 @@ def main():
                      memory_space=_capi.MEM_DEVICE)
     # descriptors are built once, as a C++ caller's Arguments would be; a step is one call
     descs = [op.describe(wl.arguments(op, b)) for b in sets]
+    prepared = []
+    if args.prepared_b and wl.kind == "mx":
+        prepared = [c.PreparedB(op, wl.arguments(op, b)) for b in sets]
 
-    def step(i):
+    def direct_step(i):
         st = op.run(descs[i % n_sets])
         if st != c.Status.kSuccess:
             raise RuntimeError(f"GEMM failed: {st!r}: {_capi.last_error()}")
+
+    step = direct_step
+    graph, launches_per_trip = None, 0
+    if args.graph:
+        # Capture one call per operand set on torch's capture stream; the library's calls
+        # are plain kernel launches once its workspace for that stream exists (the first
+        # capture pass below creates it; relaxed mode permits that allocation).
+        args.steps = max(n_sets, args.steps // n_sets * n_sets)
+        args.warmup = max(n_sets, args.warmup // n_sets * n_sets)
+        for i in range(n_sets):  # the prepared-B copies and tensor maps exist before capture
+            direct_step(i)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        launches_before_capture = c.launch_count()
+        with torch.cuda.graph(graph, capture_error_mode="relaxed"):
+            cap_stream = torch.cuda.current_stream().cuda_stream
+            op_g = wl.operator(stream=cap_stream, asynchronous=True, tile_n=args.tile_n,
+                               memory_space=_capi.MEM_DEVICE)
+            for b in sets:
+                st = op_g.run(op_g.describe(wl.arguments(op_g, b)))
+                if st != c.Status.kSuccess:
+                    raise RuntimeError(f"GEMM failed during capture: {st!r}: {_capi.last_error()}")
+
+        launches_per_trip = c.launch_count() - launches_before_capture
+
+        def step(i):  # one replay covers n_sets steps
+            if i % n_sets == 0:
+                graph.replay()
 
     def barrier():
         if world > 1:
@@ -397,6 +434,8 @@ def main():
     ev1.record()
     barrier()
     launches = c.launch_count() - launches0
+    if graph is not None:  # replayed launches do not pass through the library's counter
+        launches = launches_per_trip * (args.steps // n_sets)
     ms = ev0.elapsed_time(ev1)
     # The same K steps again, directly after the timed region, with the library's
     # per-launch events around the tensor-core kernel (on the launching stream): the
@@ -405,7 +444,7 @@ def main():
     import ctypes as C
     lib.cpuops_b200_profile(1)
     for i in range(args.steps):
-        step(i)
+        direct_step(i)
     barrier()
     t_wall1 = time.perf_counter()
     lib.cpuops_b200_profile(0)
@@ -479,7 +518,8 @@ def main():
             "config": dict(config_of(wl, world), kernel_plan={
                 "tile": f"{256 if plan.pair else 128}x{plan.tile_n}", "cta_pair": bool(plan.pair),
                 "operands_swapped": bool(plan.swapped), "k_slices": plan.slices,
-                "smem_stages": plan.stages, "ctas": plan.grid}),
+                "smem_stages": plan.stages, "ctas": plan.grid, "prepared_b": bool(plan.prepared_b),
+                "cuda_graph": bool(args.graph)}),
             "clocks": clocks,
             "gpu_launches": int(launches), "roofline": roofline, "impl": "b200",
         }

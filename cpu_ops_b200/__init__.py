@@ -9,7 +9,7 @@ from . import _capi  # noqa: F401
 from .gemm import (  # noqa: F401
     Activation, BiasAdd, Clamp, ColumnMajor, Gelu, GemmArguments, GemmCoord, GemmMx,
     GemmMxArguments, GemmMxE2M1, GemmMxE4M3, GemmMxE5M2, GemmU8S8S32, LinearCombination,
-    LinearCombinationFused, MxTensorRef, Relu, RowMajor, ScalePerCol, ScalePerRow, Silu, Status,
+    LinearCombinationFused, MxTensorRef, PreparedB, Relu, RowMajor, ScalePerCol, ScalePerRow, Silu, Status,
     TensorRef, fp4e2m1_t, fp8e4m3_t, fp8e5m2_t, launch_count, stream_status,
 )
 

@@ -44,6 +44,8 @@ EXPORTED_SYMBOLS = (
     "cpuops_b200_profile_collect",
     "cpuops_b200_launch_count",
     "cpuops_b200_last_plan",
+    "cpuops_b200_prepare_b",
+    "cpuops_b200_release_b",
     "cpuops_b200_last_error",
     "cpuops_b200_abi_version",
     "cpuops_b200_device_count",
@@ -54,7 +56,7 @@ class Plan(C.Structure):
     """cpuops_b200_plan: what the last GEMM call launched (diagnostics)."""
     _fields_ = [("swapped", C.c_int32), ("tile_n", C.c_int32), ("pair", C.c_int32),
                 ("slices", C.c_int32), ("stages", C.c_int32), ("grid", C.c_int32),
-                ("c_ring", C.c_int32), ("reserved", C.c_int32)]
+                ("c_ring", C.c_int32), ("prepared_b", C.c_int32)]
 
 
 class Scalar(C.Union):
@@ -113,6 +115,10 @@ def load() -> C.CDLL:
     lib.cpuops_b200_profile_collect.restype = C.c_int
     lib.cpuops_b200_profile_collect.argtypes = [C.POINTER(C.c_double), C.POINTER(C.c_int32)]
     lib.cpuops_b200_launch_count.restype = C.c_uint64
+    lib.cpuops_b200_prepare_b.restype = C.c_int
+    lib.cpuops_b200_prepare_b.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+    lib.cpuops_b200_release_b.restype = C.c_int
+    lib.cpuops_b200_release_b.argtypes = [C.c_void_p]
     lib.cpuops_b200_last_plan.restype = C.c_int
     lib.cpuops_b200_last_plan.argtypes = [C.POINTER(Plan)]
     lib.cpuops_b200_last_error.restype = C.c_char_p

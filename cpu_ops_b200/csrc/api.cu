@@ -90,6 +90,30 @@ unsigned long long* g_clk_buf = nullptr;  // experiments only (CPUOPS_B200_CLK)
 
 cpuops_b200_plan g_last_plan = {};
 
+// "Prepared B": a caller that keeps its weights (the B operand) unchanged over many calls
+// registers B's scale array once; the library then keeps the tile-ordered copies it builds
+// from it (one per layout a later call needs) instead of re-laying it out on every call.
+struct PreparedLayout {
+  int tile_rows, bps, tiles;  // layout identity: rows per tile, scale blocks per k-block, row tiles
+  uint8_t* atoms;             // device buffer of 512-byte atoms, owned
+  size_t bytes;
+};
+struct PreparedB {
+  int device;
+  const void* scales;
+  int n, k, ld_scales;
+  std::vector<PreparedLayout> layouts;
+};
+std::vector<PreparedB*> g_prepared;  // guarded by g_mu
+
+PreparedB* find_prepared(int device, const void* scales, int n, int k, int ld_scales) {
+  for (PreparedB* pb : g_prepared)
+    if (pb->device == device && pb->scales == scales && pb->n == n && pb->k == k &&
+        pb->ld_scales == ld_scales)
+      return pb;
+  return nullptr;
+}
+
 std::mutex g_mu;  // serialises calls (the CPU library serialises on its pool mutex too)
 DeviceState g_dev[64];
 EncodeTiledFn g_encode = nullptr;
@@ -438,6 +462,48 @@ CPUOPS_B200_API int cpuops_b200_abi_version(void) { return CPUOPS_B200_ABI_VERSI
 CPUOPS_B200_API const char* cpuops_b200_last_error(void) { return g_last_error; }
 
 CPUOPS_B200_API uint64_t cpuops_b200_launch_count(void) { return g_launches.load(); }
+
+CPUOPS_B200_API int cpuops_b200_prepare_b(const cpuops_b200_gemm_desc* d, void** handle) {
+  if (!d || !handle || d->struct_size != sizeof(cpuops_b200_gemm_desc)) return CPUOPS_B200_STATUS_BAD_DESCRIPTOR;
+  if (d->kind != CPUOPS_B200_KIND_MX) {
+    set_error("prepare_b: only MX operands carry scales to prepare");
+    return CPUOPS_B200_STATUS_UNSUPPORTED;
+  }
+  if (!d->b_scales || d->n <= 0 || d->k <= 0 || d->ld_scales_b < (d->k + 31) / 32) {
+    set_error("prepare_b: invalid B scale description");
+    return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+  }
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceState* st = nullptr;
+  if (int rc = init_device(d->device, &st)) return rc;
+  if (!is_device_pointer(d->b_scales, d->memory_space)) {
+    set_error("prepare_b: the B scales must live in device memory");
+    return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+  }
+  PreparedB* pb = find_prepared(st->device, d->b_scales, d->n, d->k, d->ld_scales_b);
+  if (!pb) {
+    pb = new PreparedB{st->device, d->b_scales, d->n, d->k, d->ld_scales_b, {}};
+    g_prepared.push_back(pb);
+  }
+  *handle = pb;
+  return CPUOPS_B200_STATUS_SUCCESS;
+}
+
+CPUOPS_B200_API int cpuops_b200_release_b(void* handle) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  for (size_t i = 0; i < g_prepared.size(); ++i) {
+    if (g_prepared[i] != handle) continue;
+    PreparedB* pb = g_prepared[i];
+    cudaSetDevice(pb->device);
+    cudaDeviceSynchronize();  // no kernel may still be reading the kept copies
+    for (PreparedLayout& pl : pb->layouts) cudaFree(pl.atoms);
+    delete pb;
+    g_prepared.erase(g_prepared.begin() + static_cast<long>(i));
+    return CPUOPS_B200_STATUS_SUCCESS;
+  }
+  set_error("release_b: unknown handle");
+  return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+}
 
 CPUOPS_B200_API int cpuops_b200_last_plan(cpuops_b200_plan* out) {
   if (!out) return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
@@ -1049,6 +1115,9 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     CUDA_TRY(cudaGetLastError());
   } else {
     // ---- scales -> tile-ordered layout (MX) ------------------------------------------------
+    const uint8_t* sfa_dev = nullptr;  // tile-ordered scale atoms of the kernel-view A / B side
+    const uint8_t* sfb_dev = nullptr;
+    bool used_prepared = false;
     const uint8_t* ak_ptr = swap ? b_ptr : a_ptr;  // kernel-view A (M side), B (N side)
     const uint8_t* bk_ptr = swap ? a_ptr : b_ptr;
     const Matrix& AkM = swap ? B : A;
@@ -1064,9 +1133,41 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
       const int ldsbk = swap ? d->ld_scales_a : d->ld_scales_b;
       ScaleLayout La = make_scale_layout(Mk, k, ldsak, kTileM, bps);
       if (ch.pair) La.tiles = 2 * ((Mk + 255) / 256);  // rows past Mk read as scale 1.0
-      if (int rc = launch_relayout(sak, wsp + off_sfa, La, sbk, wsp + off_sfb,
-                                   make_scale_layout(Nk, k, ldsbk, ch.BN, bps), stream))
+      const ScaleLayout Lb = make_scale_layout(Nk, k, ldsbk, ch.BN, bps);
+      sfa_dev = wsp + off_sfa;
+      sfb_dev = wsp + off_sfb;
+      // The caller's B scales (kernel-view A side when the operands are swapped): use the
+      // kept copy when B was registered with cpuops_b200_prepare_b, building it on first use.
+      PreparedB* pb = sb_dev ? find_prepared(st.device, d->b_scales, n, k, d->ld_scales_b) : nullptr;
+      if (pb) {
+        const ScaleLayout& L = swap ? La : Lb;
+        PreparedLayout* have = nullptr;
+        for (PreparedLayout& pl : pb->layouts)
+          if (pl.tile_rows == L.tile_rows && pl.bps == L.bps && pl.tiles == L.tiles) have = &pl;
+        if (!have) {
+          PreparedLayout pl;
+          pl.tile_rows = L.tile_rows;
+          pl.bps = L.bps;
+          pl.tiles = L.tiles;
+          pl.bytes = static_cast<size_t>(relayout_work_items(L)) * 4 * 512;
+          CUDA_TRY(cudaMalloc(&pl.atoms, pl.bytes));
+          if (int rc = launch_relayout(swap ? sak : sbk, pl.atoms, L, nullptr, nullptr, L, stream)) return rc;
+          // once, so that calls on any stream may use the copy from now on
+          CUDA_TRY(cudaStreamSynchronize(stream));
+          pb->layouts.push_back(pl);
+          have = &pb->layouts.back();
+        }
+        if (swap) {
+          sfa_dev = have->atoms;
+          if (int rc = launch_relayout(sbk, wsp + off_sfb, Lb, nullptr, nullptr, Lb, stream)) return rc;
+        } else {
+          sfb_dev = have->atoms;
+          if (int rc = launch_relayout(sak, wsp + off_sfa, La, nullptr, nullptr, La, stream)) return rc;
+        }
+        used_prepared = true;
+      } else if (int rc = launch_relayout(sak, wsp + off_sfa, La, sbk, wsp + off_sfb, Lb, stream)) {
         return rc;
+      }
     }
 
     // ---- tensor maps -----------------------------------------------------------------------
@@ -1137,8 +1238,8 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
       }
     }
     if (is_mx) {
-      p.sfa = wsp + off_sfa;
-      p.sfb = wsp + off_sfb;
+      p.sfa = sfa_dev;
+      p.sfb = sfb_dev;
       p.sfa_stage_bytes = (bps / 4) * 512;
       p.sfb_stage_bytes = (bps / 4) * ((ch.BN + 127) / 128) * 512;
       const int sf_cols = (p.sfa_stage_bytes + p.sfb_stage_bytes) / 512 * 4;
@@ -1254,6 +1355,7 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     g_last_plan.stages = stages;
     g_last_plan.grid = static_cast<int32_t>(grid);
     g_last_plan.c_ring = p.c_ring;
+    g_last_plan.prepared_b = used_prepared ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
     if (kind == kKindI8) {

@@ -341,6 +341,29 @@ class GemmMx(_Operator):
         return self._finish(desc, args)
 
 
+class PreparedB:
+    """Keeps the tile-ordered copy of an MX weight operand's scales across calls
+    (``cpuops_b200_prepare_b``): a decode loop registers its weights once."""
+
+    def __init__(self, op: "GemmMx", args: "GemmMxArguments"):
+        self._handle = C.c_void_p()
+        desc = op.describe(args)
+        st = _capi.load().cpuops_b200_prepare_b(C.byref(desc), C.byref(self._handle))
+        if st != 0:
+            raise RuntimeError(f"prepare_b failed ({st}): {_capi.last_error()}")
+
+    def release(self) -> None:
+        if self._handle:
+            _capi.load().cpuops_b200_release_b(self._handle)
+            self._handle = C.c_void_p()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.release()
+
+
 def GemmMxE4M3(layout_c=RowMajor, **kw):
     """gemm_mx.h:121-122."""
     return GemmMx(fp8e4m3_t, fp8e4m3_t, layout_c, **kw)

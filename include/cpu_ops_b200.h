@@ -215,6 +215,17 @@ CPUOPS_B200_API int cpuops_b200_stream_status(void* stream);
 CPUOPS_B200_API int cpuops_b200_profile(int enable);
 CPUOPS_B200_API int cpuops_b200_profile_collect(double* total_ms, int32_t* launches);
 
+/* Prepared B (no counterpart in the reference, whose calls are stateless): a decode loop
+ * multiplies ever-new activations by the same MX weights.  prepare_b registers the B
+ * scale array described by `d` (b_scales, n, k, ld_scales_b; device memory) as unchanged
+ * until release_b: later cpuops_b200_gemm calls that pass the same b_scales / n / k /
+ * ld_scales_b keep the tile-ordered copy of those scales that the tensor cores need
+ * (built on the first such call, one per tile layout) instead of rebuilding it per call.
+ * The caller must not modify the scale array while it is registered.  release_b
+ * synchronises the device and frees the copies. */
+CPUOPS_B200_API int cpuops_b200_prepare_b(const cpuops_b200_gemm_desc* d, void** handle);
+CPUOPS_B200_API int cpuops_b200_release_b(void* handle);
+
 /* What the last cpuops_b200_gemm call of this process that reached the tensor-core kernel
  * launched (diagnostics for tests and benchmarks): */
 typedef struct cpuops_b200_plan {
@@ -225,7 +236,7 @@ typedef struct cpuops_b200_plan {
   int32_t stages;    /* shared-memory pipeline depth                              */
   int32_t grid;      /* CTAs launched                                             */
   int32_t c_ring;    /* 1: C prefetched by TMA into shared memory                  */
-  int32_t reserved;
+  int32_t prepared_b; /* 1: B's scale atoms came from cpuops_b200_prepare_b        */
 } cpuops_b200_plan;
 CPUOPS_B200_API int cpuops_b200_last_plan(cpuops_b200_plan* out);
 
