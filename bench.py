@@ -327,6 +327,9 @@ def main():
     ap.add_argument("--tile-n", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--gather", action="store_true",
+                    help="N > 1: every step also all-gathers the ranks' D row blocks into a replicated D "
+                         "(NCCL, on a second stream so that it overlaps the next step's GEMM)")
     ap.add_argument("--graph", action="store_true",
                     help="replay the calls from a CUDA graph (one trip round the operand ring per "
                          "replay), as a launch-bound decode loop would; steps are rounded to whole trips")
@@ -379,10 +382,30 @@ def main():
     if args.prepared_b and wl.kind == "mx":
         prepared = [c.PreparedB(op, wl.arguments(op, b)) for b in sets]
 
+    gather_stream, gather_events, gather_done, d_full = None, [], [], None
+    if args.gather and world > 1:
+        # equal blocks (every rank holds wl.m rows): in-place all-gather into a full-size D
+        gather_stream = torch.cuda.Stream(device=dev)
+        gather_events = [torch.cuda.Event() for _ in range(n_sets)]
+        gather_done = [None] * n_sets  # set j's D may be overwritten once its gather has read it
+        d_full = [torch.empty((world * wl.m * wl.n,), dtype=sets[0]["D"].dtype, device=dev)
+                  for _ in range(2)]
+
     def direct_step(i):
-        st = op.run(descs[i % n_sets])
+        j = i % n_sets
+        if gather_stream is not None and gather_done[j] is not None:
+            torch.cuda.current_stream().wait_event(gather_done[j])
+        st = op.run(descs[j])
         if st != c.Status.kSuccess:
             raise RuntimeError(f"GEMM failed: {st!r}: {_capi.last_error()}")
+        if gather_stream is not None:
+            gather_events[j].record(torch.cuda.current_stream())
+            with torch.cuda.stream(gather_stream):
+                gather_stream.wait_event(gather_events[j])
+                dist.all_gather_into_tensor(d_full[i % 2], sets[j]["D"])
+                if gather_done[j] is None:
+                    gather_done[j] = torch.cuda.Event()
+                gather_done[j].record(gather_stream)
 
     step = direct_step
     graph, launches_per_trip = None, 0
@@ -431,6 +454,8 @@ def main():
     ev0.record()
     for i in range(args.steps):
         step(i)
+    if gather_stream is not None:
+        torch.cuda.current_stream().wait_stream(gather_stream)
     ev1.record()
     barrier()
     launches = c.launch_count() - launches0
@@ -519,7 +544,10 @@ def main():
                 "tile": f"{256 if plan.pair else 128}x{plan.tile_n}", "cta_pair": bool(plan.pair),
                 "operands_swapped": bool(plan.swapped), "k_slices": plan.slices,
                 "smem_stages": plan.stages, "ctas": plan.grid, "prepared_b": bool(plan.prepared_b),
-                "cuda_graph": bool(args.graph)}),
+                "cuda_graph": bool(args.graph)},
+                gather_d=bool(args.gather and world > 1),
+                seeds=f"operand set s of rank r: 1000*r + s (numpy PCG64 streams per operand, "
+                      f"cpu_ops_b200/workloads.py)"),
             "clocks": clocks,
             "gpu_launches": int(launches), "roofline": roofline, "impl": "b200",
         }
