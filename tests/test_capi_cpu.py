@@ -120,3 +120,31 @@ def test_scale_layout_bytes(lib):
     assert f(128, 33, 128, 4) == 128 * 4               # k padded to one stage of 4 blocks
     assert f(192, 256, 192, 8) == 2 * 512 * 2          # 192-row tile = two 128-row atoms, 8 blocks
     assert f(0, 10, 128, 4) == 0 and f(10, 10, 128, 5) == 0
+
+
+def test_prepare_b_validates_before_touching_a_device(lib):
+    """cpuops_b200_prepare_b: int8 operands carry no scales; a bad scale description
+    is rejected; without a device a valid registration fails loudly."""
+    handle = C.c_void_p()
+    d = _capi.GemmDesc()
+    d.struct_size = C.sizeof(_capi.GemmDesc)
+    d.kind = _capi.KIND_I8
+    assert lib.cpuops_b200_prepare_b(C.byref(d), C.byref(handle)) == _capi.STATUS_UNSUPPORTED
+    d.kind = _capi.KIND_MX
+    d.n, d.k, d.ld_scales_b = 8, 64, 1          # needs two scale entries per row
+    scales = np.zeros(16, np.uint8)
+    d.b_scales = scales.ctypes.data
+    assert lib.cpuops_b200_prepare_b(C.byref(d), C.byref(handle)) == _capi.STATUS_INVALID_ARGUMENTS
+    d.ld_scales_b = 2
+    d.struct_size = 8
+    assert lib.cpuops_b200_prepare_b(C.byref(d), C.byref(handle)) == _capi.STATUS_BAD_DESCRIPTOR
+    d.struct_size = C.sizeof(_capi.GemmDesc)
+    if lib.cpuops_b200_device_count() == 0:
+        assert lib.cpuops_b200_prepare_b(C.byref(d), C.byref(handle)) == _capi.STATUS_NO_DEVICE
+    assert lib.cpuops_b200_release_b(None) == _capi.STATUS_INVALID_ARGUMENTS
+
+
+def test_last_plan_is_readable_before_any_call(lib):
+    plan = _capi.Plan()
+    assert lib.cpuops_b200_last_plan(C.byref(plan)) == 0
+    assert lib.cpuops_b200_last_plan(None) == _capi.STATUS_INVALID_ARGUMENTS
