@@ -613,7 +613,7 @@ CPUOPS_B200_API int cpuops_b200_debug_clock(unsigned long long* out) {
   if (!g_clk_buf || !out) return 1;
   cudaDeviceSynchronize();
   // [8],[9]: first CTA start / last CTA end (ns)
-  cudaMemcpy(out, g_clk_buf, 10 * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+  cudaMemcpy(out, g_clk_buf, 12 * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
   return 0;
 }
 

@@ -270,6 +270,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       // The scale atoms come from the re-layout kernel launched just before this one,
       // which may still be running (programmatic stream serialization).
       if constexpr (kMx) asm volatile("griddepcontrol.wait;" ::: "memory");
+      const bool pdbg = p.clk_dbg != nullptr && blockIdx.x == 0;
+      long long pdbg_wait = 0;
+      const long long pdbg_start = pdbg ? clock64() : 0;
       for (int t = work0; t < total_tiles && ok; t += work_step) {
         const TileCoord tc = decode_tile(p, t);
         const int m_tile128 = tc.m_tile * kCtas + static_cast<int>(cta_rank);  // this CTA's 128 rows
@@ -283,11 +286,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           sfb_base = p.sfb + static_cast<int64_t>(tc.n_tile) * p.k_blocks * p.sfb_stage_bytes;
         }
         for (int i = 0; i < tc.nkb; ++i, kx += 128) {
+          const long long pw0 = pdbg ? clock64() : 0;
           if (!peek && !__all_sync(0xffffffffu, mbar_wait_bounded(empty_addr, ph ^ 1u, abort_flag))) {
             if (el) record_error(p, abort_flag, kErrProducerWait);
             ok = false;
             break;
           }
+          if (pdbg) pdbg_wait += clock64() - pw0;
           {
             // probe the next stage's barrier now; the answer is used on the next trip
             const bool wrap = s + 1 == stages;
@@ -338,6 +343,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             sf_dst += sf_stage;
           }
         }
+      }
+      if (pdbg && el) {
+        p.clk_dbg[10] = static_cast<unsigned long long>(clock64() - pdbg_start);
+        p.clk_dbg[11] = static_cast<unsigned long long>(pdbg_wait);
       }
       if (*abort_flag != 0 && el) {
         // Let copies that were already issued land before the CTA exits.
