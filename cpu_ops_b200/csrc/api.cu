@@ -8,387 +8,17 @@
 // persistent grid of CTA tiles, the per-task pack buffers disappear (TMA feeds
 // the tensor cores from the caller's layout), the split-k workspace lives in a
 // cached device buffer.
-#include <cuda.h>
-#include <cuda_runtime.h>
-
 #include <algorithm>
-#include <atomic>
-#include <cstdarg>
-#include <cstdio>
-#include <cstdlib>
-#include <cstring>
-#include <map>
-#include <mutex>
-#include <vector>
+#include <cmath>
 
-#include "../../include/cpu_ops_b200.h"
 #include "aux_kernels.cuh"
 #include "gemm_kernel.cuh"
-#include "gemm_params.h"
+#include "host_runtime.h"
+#include "tensor_maps.h"
 
 namespace {
 
 using namespace b200;
-
-thread_local char g_last_error[512] = "";
-std::atomic<uint64_t> g_launches{0};
-
-void set_error(const char* fmt, ...) {
-  va_list ap;
-  va_start(ap, fmt);
-  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
-  va_end(ap);
-}
-
-#define CUDA_TRY(expr)                                                                       \
-  do {                                                                                       \
-    cudaError_t err__ = (expr);                                                              \
-    if (err__ != cudaSuccess) {                                                              \
-      set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(err__), __FILE__, __LINE__); \
-      return CPUOPS_B200_STATUS_CUDA_ERROR;                                                  \
-    }                                                                                        \
-  } while (0)
-
-// ---- per-device state ---------------------------------------------------------
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-
-struct DeviceState {
-  bool ready = false;
-  int device = -1;
-  int sm_count = 0;
-  int smem_optin = 0;
-  cudaStream_t stream = nullptr;  // the library's own stream
-  int32_t* error_dev = nullptr;   // device error word
-  int32_t* error_host = nullptr;  // pinned mirror
-  // grow-only workspaces, one per stream that ever called in
-  struct Workspace {
-    void* ptr = nullptr;
-    size_t bytes = 0;
-  };
-  std::map<cudaStream_t, Workspace> ws;
-  // Host-operand calls are cut into row panels that run on these streams, so that one
-  // panel's upload, another's GEMM and a third's download overlap (see gemm_body).
-  static constexpr int kPanelStreams = 3;
-  cudaStream_t panel_stream[kPanelStreams] = {nullptr, nullptr, nullptr};
-  cudaEvent_t panel_done[kPanelStreams] = {nullptr, nullptr, nullptr};
-  cudaEvent_t fork_event = nullptr;
-  // Largest number of two-CTA clusters of the pair kernel that can be resident at once,
-  // per kind (-1: not asked yet; 0: cluster launch unavailable).
-  int pair_clusters[3] = {-1, -1, -1};
-};
-
-// Optional timing of the tensor-core kernel alone (events on the launching stream).
-bool g_profile = false;
-std::vector<std::pair<cudaEvent_t, cudaEvent_t>> g_profile_events;
-
-unsigned long long* g_clk_buf = nullptr;  // experiments only (CPUOPS_B200_CLK)
-
-cpuops_b200_plan g_last_plan = {};
-
-// "Prepared B": a caller that keeps its weights (the B operand) unchanged over many calls
-// registers B's scale array once; the library then keeps the tile-ordered copies it builds
-// from it (one per layout a later call needs) instead of re-laying it out on every call.
-struct PreparedLayout {
-  int tile_rows, bps, tiles;  // layout identity: rows per tile, scale blocks per k-block, row tiles
-  uint8_t* atoms;             // device buffer of 512-byte atoms, owned
-  size_t bytes;
-};
-struct PreparedB {
-  int device;
-  const void* scales;
-  int n, k, ld_scales;
-  std::vector<PreparedLayout> layouts;
-};
-std::vector<PreparedB*> g_prepared;  // guarded by g_mu
-
-PreparedB* find_prepared(int device, const void* scales, int n, int k, int ld_scales) {
-  for (PreparedB* pb : g_prepared)
-    if (pb->device == device && pb->scales == scales && pb->n == n && pb->k == k &&
-        pb->ld_scales == ld_scales)
-      return pb;
-  return nullptr;
-}
-
-std::mutex g_mu;  // serialises calls (the CPU library serialises on its pool mutex too)
-DeviceState g_dev[64];
-EncodeTiledFn g_encode = nullptr;
-int g_device_count = -2;  // -2: not probed
-
-int probe_devices() {
-  if (g_device_count != -2) return g_device_count;
-  int n = 0;
-  if (cudaGetDeviceCount(&n) != cudaSuccess) {
-    cudaGetLastError();
-    g_device_count = 0;
-    return 0;
-  }
-  int usable = 0;
-  for (int d = 0; d < n && d < 64; ++d) {
-    int major = 0;
-    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, d) == cudaSuccess &&
-        major == 10)
-      ++usable;
-  }
-  g_device_count = usable;
-  return usable;
-}
-
-int init_device(int device, DeviceState** out) {
-  if (probe_devices() <= 0) {
-    set_error("no sm_100 CUDA device is available; this library has no CPU fallback");
-    return CPUOPS_B200_STATUS_NO_DEVICE;
-  }
-  if (device < 0) CUDA_TRY(cudaGetDevice(&device));
-  if (device >= 64) {
-    set_error("device ordinal %d out of range", device);
-    return CPUOPS_B200_STATUS_BAD_DESCRIPTOR;
-  }
-  DeviceState& st = g_dev[device];
-  if (!st.ready) {
-    int major = 0;
-    CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
-    if (major != 10) {
-      set_error("device %d is not sm_100 (compute capability major %d)", device, major);
-      return CPUOPS_B200_STATUS_NO_DEVICE;
-    }
-    CUDA_TRY(cudaSetDevice(device));
-    st.device = device;
-    CUDA_TRY(cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, device));
-    CUDA_TRY(cudaDeviceGetAttribute(&st.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
-    CUDA_TRY(cudaStreamCreateWithFlags(&st.stream, cudaStreamNonBlocking));
-    for (int j = 0; j < DeviceState::kPanelStreams; ++j) {
-      CUDA_TRY(cudaStreamCreateWithFlags(&st.panel_stream[j], cudaStreamNonBlocking));
-      CUDA_TRY(cudaEventCreateWithFlags(&st.panel_done[j], cudaEventDisableTiming));
-    }
-    CUDA_TRY(cudaEventCreateWithFlags(&st.fork_event, cudaEventDisableTiming));
-    CUDA_TRY(cudaMalloc(&st.error_dev, sizeof(int32_t)));
-    CUDA_TRY(cudaMemset(st.error_dev, 0, sizeof(int32_t)));
-    CUDA_TRY(cudaMallocHost(&st.error_host, sizeof(int32_t)));
-    *st.error_host = 0;
-    if (!g_encode) {
-      void* fn = nullptr;
-      cudaDriverEntryPointQueryResult qres;
-      CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
-      if (!fn || qres != cudaDriverEntryPointSuccess) {
-        set_error("cuTensorMapEncodeTiled is not exported by this driver");
-        return CPUOPS_B200_STATUS_CUDA_ERROR;
-      }
-      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
-    }
-    CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindI8, false>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
-    CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindMxf8, false>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
-    CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindMxf4, false>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
-    CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindI8, true>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
-    CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindMxf8, true>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
-    CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindMxf4, true>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
-    st.ready = true;
-  } else {
-    CUDA_TRY(cudaSetDevice(device));
-  }
-  *out = &st;
-  return 0;
-}
-
-int ensure_workspace(DeviceState& st, cudaStream_t stream, size_t bytes, uint8_t** out) {
-  DeviceState::Workspace& w = st.ws[stream];
-  if (w.bytes < bytes) {
-    if (w.ptr) {
-      CUDA_TRY(cudaStreamSynchronize(stream));
-      CUDA_TRY(cudaFree(w.ptr));
-      w.ptr = nullptr;
-      w.bytes = 0;
-    }
-    const size_t want = std::max(bytes, static_cast<size_t>(1) << 20);
-    CUDA_TRY(cudaMalloc(&w.ptr, want));
-    w.bytes = want;
-  }
-  *out = static_cast<uint8_t*>(w.ptr);
-  return 0;
-}
-
-size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
-
-// Experiment switches, read from the environment once.
-struct EnvSwitches {
-  bool no_c_ring = getenv("CPUOPS_B200_NO_C_RING") != nullptr;
-  bool no_d_tma = getenv("CPUOPS_B200_NO_D_TMA") != nullptr;
-  bool clk = getenv("CPUOPS_B200_CLK") != nullptr;
-  int debug_flags = getenv("CPUOPS_B200_DEBUG") ? atoi(getenv("CPUOPS_B200_DEBUG")) : 0;
-  int raster_m = getenv("CPUOPS_B200_RASTER") ? atoi(getenv("CPUOPS_B200_RASTER")) : 0;
-  int pair = getenv("CPUOPS_B200_PAIR") ? atoi(getenv("CPUOPS_B200_PAIR")) : -1;  // -1: heuristic
-};
-const EnvSwitches& env_switches() {
-  static const EnvSwitches e;
-  return e;
-}
-
-// ---- tensor maps --------------------------------------------------------------
-
-// A tensor map is a pure function of its encode arguments, and a caller that repeats
-// a GEMM on the same buffers (a decode loop) asks for the same few maps again and
-// again: a small direct-mapped cache saves the driver call (about a microsecond each).
-// Guarded by g_mu like the rest of the call.
-struct TensorMapKey {
-  uint64_t base, d0, d1, pitch;
-  uint32_t box1, words;
-  bool operator==(const TensorMapKey& o) const {
-    return base == o.base && d0 == o.d0 && d1 == o.d1 && pitch == o.pitch && box1 == o.box1 &&
-           words == o.words;
-  }
-};
-struct TensorMapSlot {
-  bool valid = false;
-  TensorMapKey key;
-  CUtensorMap map;
-};
-constexpr int kTensorMapSlots = 64;
-TensorMapSlot g_tm_cache[kTensorMapSlots];
-
-TensorMapSlot& tensor_map_slot(const TensorMapKey& k) {
-  uint64_t h = k.base * 0x9E3779B97F4A7C15ull;
-  h ^= (k.d0 + 0x632BE59BD9B4E019ull) * 0xC2B2AE3D27D4EB4Full;
-  h ^= (k.d1 * 31 + k.pitch * 17 + k.box1 * 7 + k.words) * 0x165667B19E3779F9ull;
-  return g_tm_cache[(h >> 32) % kTensorMapSlots];
-}
-
-// 2-D byte tensor: `inner` contiguous bytes per row, `outer` rows `pitch` bytes
-// apart; 128-byte swizzled boxes of box_outer rows; out-of-range reads are zero.
-int make_tensor_map(CUtensorMap* tm, const void* base, uint64_t inner, uint64_t outer,
-                    uint64_t pitch, uint32_t box_outer) {
-  const cuuint64_t dims[2] = {inner, outer};
-  if (outer <= 1) pitch = (inner + 15) / 16 * 16;  // a single row: the pitch is never used
-  const TensorMapKey key{reinterpret_cast<uint64_t>(base), inner, outer, pitch, box_outer, 0u};
-  TensorMapSlot& slot = tensor_map_slot(key);
-  if (slot.valid && slot.key == key) {
-    *tm = slot.map;
-    return 0;
-  }
-  const cuuint64_t strides[1] = {pitch};
-  const cuuint32_t box[2] = {128, box_outer};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r =
-      g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
-               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    set_error("cuTensorMapEncodeTiled failed with %d (base %p inner %llu outer %llu pitch %llu box %u)",
-              static_cast<int>(r), base, (unsigned long long)inner, (unsigned long long)outer,
-              (unsigned long long)pitch, box_outer);
-    return CPUOPS_B200_STATUS_CUDA_ERROR;
-  }
-  slot.valid = true;
-  slot.key = key;
-  slot.map = *tm;
-  return 0;
-}
-
-// 2-D tensor of 32-bit words (C): 32 x 32 boxes, 128-byte swizzled rows.
-int make_tensor_map_words(CUtensorMap* tm, const void* base, uint64_t cols, uint64_t rows,
-                          uint64_t pitch_bytes) {
-  const cuuint64_t dims[2] = {cols, rows};
-  if (rows <= 1) pitch_bytes = (cols * 4 + 15) / 16 * 16;
-  const TensorMapKey key{reinterpret_cast<uint64_t>(base), cols, rows, pitch_bytes, 32u, 1u};
-  TensorMapSlot& slot = tensor_map_slot(key);
-  if (slot.valid && slot.key == key) {
-    *tm = slot.map;
-    return 0;
-  }
-  const cuuint64_t strides[1] = {pitch_bytes};
-  const cuuint32_t box[2] = {32, 32};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r =
-      g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box,
-               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    set_error("cuTensorMapEncodeTiled (C) failed with %d", static_cast<int>(r));
-    return CPUOPS_B200_STATUS_CUDA_ERROR;
-  }
-  slot.valid = true;
-  slot.key = key;
-  slot.map = *tm;
-  return 0;
-}
-
-// Packed 4-bit rows (k elements, two per byte) read as 128-element boxes that land in
-// shared memory in the padded form kind::mxf8f6f4 takes: 16 elements per 16 bytes, so a
-// box row is 128 bytes and the 128-byte swizzle applies as for 8-bit operands.  The
-// driver requires a 32-byte aligned base and pitch and an inner extent that is a
-// multiple of 128 elements: the extent is rounded up, and the caller guarantees that
-// the rounded row still lies inside the pitch.
-int make_tensor_map_fp4_padded(CUtensorMap* tm, const void* base, uint64_t k_elems, uint64_t outer,
-                               uint64_t pitch, uint32_t box_outer) {
-  const uint64_t k128 = (k_elems + 127) / 128 * 128;
-  if (outer <= 1) pitch = k128 / 2;
-  const TensorMapKey key{reinterpret_cast<uint64_t>(base), k128, outer, pitch, box_outer, 3u};
-  TensorMapSlot& slot = tensor_map_slot(key);
-  if (slot.valid && slot.key == key) {
-    *tm = slot.map;
-    return 0;
-  }
-  const cuuint64_t dims[2] = {k128, outer};
-  const cuuint64_t strides[1] = {pitch};
-  const cuuint32_t box[2] = {128, box_outer};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r =
-      g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, const_cast<void*>(base), dims, strides,
-               box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    set_error("cuTensorMapEncodeTiled (padded fp4) failed with %d (base %p k %llu outer %llu pitch %llu)",
-              static_cast<int>(r), base, (unsigned long long)k128, (unsigned long long)outer,
-              (unsigned long long)pitch);
-    return CPUOPS_B200_STATUS_CUDA_ERROR;
-  }
-  slot.valid = true;
-  slot.key = key;
-  slot.map = *tm;
-  return 0;
-}
-
-// The re-laid-out scale array as rows of one 512-byte atom each (128 words, not
-// swizzled); a box is the `box_atoms` atoms of one k-block.
-int make_tensor_map_atoms(CUtensorMap* tm, const void* base, uint64_t n_atoms, uint32_t box_atoms) {
-  const TensorMapKey key{reinterpret_cast<uint64_t>(base), 128, n_atoms, 512, box_atoms, 2u};
-  TensorMapSlot& slot = tensor_map_slot(key);
-  if (slot.valid && slot.key == key) {
-    *tm = slot.map;
-    return 0;
-  }
-  const cuuint64_t dims[2] = {128, n_atoms};
-  const cuuint64_t strides[1] = {512};
-  const cuuint32_t box[2] = {128, box_atoms};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r =
-      g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box,
-               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    set_error("cuTensorMapEncodeTiled (scale atoms) failed with %d", static_cast<int>(r));
-    return CPUOPS_B200_STATUS_CUDA_ERROR;
-  }
-  slot.valid = true;
-  slot.key = key;
-  slot.map = *tm;
-  return 0;
-}
-
-bool tma_addressable(const void* base, int64_t pitch_bytes, int64_t outer) {
-  if (reinterpret_cast<uintptr_t>(base) & 15u) return false;
-  if (outer > 1 && (pitch_bytes & 15)) return false;
-  return true;
-}
 
 // ---- memory space ---------------------------------------------------------------
 
@@ -876,7 +506,8 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     sub.flags |= CPUOPS_B200_FLAG_ASYNC;
     sub.split_k_slices = 1;
     sub.tile_n = ch.BN;
-    const int n_panels = std::max(2, std::min(8, m / 512));
+    int n_panels = std::max(2, std::min(8, m / 512));
+    if (env_switches().panels > 0) n_panels = std::max(2, std::min(env_switches().panels, m / 128));
     const int panel_rows = static_cast<int>(align_up((m + n_panels - 1) / n_panels, 128));
     int issued = 0;
     for (int row0 = 0; row0 < m; row0 += panel_rows, ++issued) {
