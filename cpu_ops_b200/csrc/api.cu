@@ -288,7 +288,11 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
 
 }  // extern "C"
 
-static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
+// Descriptor checks that need no device, in the CPU library's order (gemm.h:100-122,
+// gemm_mx.h:79-112).  Returns a status; *finished is set when that status is final (an
+// error, or the empty problem, which succeeds without touching anything).
+static int validate_descriptor(const cpuops_b200_gemm_desc* d, bool* finished) {
+  *finished = true;
   if (!d || d->struct_size != sizeof(cpuops_b200_gemm_desc)) {
     set_error("descriptor is null or struct_size does not match this library (ABI %d)",
               CPUOPS_B200_ABI_VERSION);
@@ -313,8 +317,6 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     set_error("n_ops out of range");
     return CPUOPS_B200_STATUS_BAD_DESCRIPTOR;
   }
-
-  // ---- validation, in the CPU library's order (gemm.h:100-122, gemm_mx.h:79-112) ----
   const int m = d->m, n = d->n, k = d->k;
   if (m < 0 || n < 0 || k < 0) return CPUOPS_B200_STATUS_INVALID_PROBLEM;
   if (m == 0 || n == 0) return CPUOPS_B200_STATUS_SUCCESS;
@@ -339,11 +341,6 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     // (gemm.h:106-110); C and D themselves are dereferenced, so they must exist.
     if (!d->c || !d->d) return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
   }
-  // fp4 x fp8 (GemmMx<SA, SB> allows any pair, gemm_mx.h:44-47): both operands go through
-  // kind::mxf8f6f4, whose 4-bit operand sits in shared memory as 16 elements per 16 bytes
-  // (8 data + 8 padding); TMA produces that form from the packed bytes (tensor-map type
-  // 16U4_ALIGN16B), so a k-block is 128 elements for both operands.
-  const bool mixed = is_mx && (fp4_a != fp4_b);
   for (int t = 0; t < d->n_ops; ++t) {
     const int oc = d->ops[t].opcode;
     if (oc < CPUOPS_B200_OP_RELU || oc > CPUOPS_B200_OP_SILU) {
@@ -358,6 +355,26 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
          oc == CPUOPS_B200_OP_SCALE_PER_COL) && !d->ops[t].ptr)
       return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
   }
+  *finished = false;
+  return CPUOPS_B200_STATUS_SUCCESS;
+}
+
+static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
+  {
+    bool finished = false;
+    const int rc = validate_descriptor(d, &finished);
+    if (finished) return rc;
+  }
+  const bool is_mx = d->kind == CPUOPS_B200_KIND_MX;
+  const int m = d->m, n = d->n, k = d->k;
+  const bool c_rm = d->c_row_major != 0;
+  const bool fp4_a = is_mx && d->a_format == CPUOPS_B200_FMT_E2M1;
+  const bool fp4_b = is_mx && d->b_format == CPUOPS_B200_FMT_E2M1;
+  // fp4 x fp8 (GemmMx<SA, SB> allows any pair, gemm_mx.h:44-47): both operands go through
+  // kind::mxf8f6f4, whose 4-bit operand sits in shared memory as 16 elements per 16 bytes
+  // (8 data + 8 padding); TMA produces that form from the packed bytes (tensor-map type
+  // 16U4_ALIGN16B), so a k-block is 128 elements for both operands.
+  const bool mixed = is_mx && (fp4_a != fp4_b);
 
   DeviceState* stp = nullptr;
   if (int rc = init_device(d->device, &stp)) return rc;
