@@ -288,6 +288,89 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
 
 }  // extern "C"
 
+// Host operands of a large problem: row panels on three streams.
+// A call whose A and D live in host memory is bound by the PCIe copies, not by the
+// GEMM.  Run serially (upload everything, compute, download everything) the two copy
+// directions never overlap.  Instead: stage the B side once, then cut the output rows
+// into panels and issue each panel as its own call (host A/C/D rows, device B) on one
+// of three streams; a panel's upload, its neighbour's GEMM and the download of the
+// one before overlap, and both copy engines stay busy.  Every panel uses the tile
+// width and the single k slice chosen for the whole problem, so each element is
+// computed exactly as the unsplit call would compute it.
+static int run_host_row_panels(const cpuops_b200_gemm_desc* d, DeviceState& st, cudaStream_t stream,
+                               const Choice& ch, const Matrix& A, const Matrix& B, bool is_mx, bool fp4_b,
+                               bool a_kmajor, bool b_dev, bool sb_dev, bool c_rm) {
+  const int m = d->m, n = d->n, k = d->k;
+  Plan bplan;
+  size_t pb = 0, psb = 0;
+  const int64_t b_pitch_staged = align_up(B.inner_bytes, 16);
+  if (!b_dev) pb = bplan.take(b_pitch_staged * B.outer);
+  if (is_mx && !sb_dev) psb = bplan.take(static_cast<size_t>(n) * d->ld_scales_b);
+  uint8_t* bw = nullptr;
+  if (bplan.total > 0) {
+    if (int rc = ensure_workspace(st, stream, bplan.total, &bw)) return rc;
+  }
+  cpuops_b200_gemm_desc sub = *d;
+  if (!b_dev) {
+    CUDA_TRY(cudaMemcpy2DAsync(bw + pb, b_pitch_staged, d->b, B.pitch, B.inner_bytes, B.outer,
+                               cudaMemcpyHostToDevice, stream));
+    sub.b = bw + pb;
+    sub.ldb = static_cast<int32_t>(fp4_b ? b_pitch_staged * 2 : b_pitch_staged);
+  }
+  if (is_mx && !sb_dev) {
+    CUDA_TRY(cudaMemcpyAsync(bw + psb, d->b_scales,
+                             static_cast<size_t>(n - 1) * d->ld_scales_b + (k + 31) / 32,
+                             cudaMemcpyHostToDevice, stream));
+    sub.b_scales = bw + psb;
+  }
+  CUDA_TRY(cudaEventRecord(st.fork_event, stream));
+  sub.memory_space = CPUOPS_B200_MEM_AUTO;
+  sub.flags |= CPUOPS_B200_FLAG_ASYNC;
+  sub.split_k_slices = 1;
+  sub.tile_n = ch.BN;
+  int n_panels = std::max(2, std::min(8, m / 512));
+  if (env_switches().panels > 0) n_panels = std::max(2, std::min(env_switches().panels, m / 128));
+  const int panel_rows = static_cast<int>(align_up((m + n_panels - 1) / n_panels, 128));
+  int issued = 0;
+  for (int row0 = 0; row0 < m; row0 += panel_rows, ++issued) {
+    const int j = issued % DeviceState::kPanelStreams;
+    if (issued < DeviceState::kPanelStreams)
+      CUDA_TRY(cudaStreamWaitEvent(st.panel_stream[j], st.fork_event, 0));
+    cpuops_b200_gemm_desc pd = sub;
+    pd.m = std::min(panel_rows, m - row0);
+    pd.stream = st.panel_stream[j];
+    // A: k-major rows of m (row pitch A.pitch bytes), or m contiguous (int8 column-major)
+    pd.a = static_cast<const uint8_t*>(d->a) + (a_kmajor ? row0 * A.pitch : static_cast<int64_t>(row0));
+    if (is_mx)
+      pd.a_scales = static_cast<const uint8_t*>(d->a_scales) + static_cast<int64_t>(row0) * d->ld_scales_a;
+    const int64_t c_off = c_rm ? static_cast<int64_t>(row0) * d->ldc : row0;
+    const int64_t d_off = c_rm ? static_cast<int64_t>(row0) * d->ldd : row0;
+    pd.c = static_cast<const uint8_t*>(d->c) + c_off * 4;
+    pd.d = static_cast<uint8_t*>(d->d) + d_off * 4;
+    for (int t = 0; t < pd.n_ops; ++t)
+      if (pd.ops[t].opcode == CPUOPS_B200_OP_SCALE_PER_ROW)
+        pd.ops[t].ptr = static_cast<const uint8_t*>(d->ops[t].ptr) + static_cast<int64_t>(row0) * 4;
+    if (int rc = gemm_body(&pd, 1)) {
+      for (int q = 0; q < DeviceState::kPanelStreams; ++q) cudaStreamSynchronize(st.panel_stream[q]);
+      return rc;
+    }
+  }
+  for (int j = 0; j < std::min(issued, static_cast<int>(DeviceState::kPanelStreams)); ++j) {
+    CUDA_TRY(cudaEventRecord(st.panel_done[j], st.panel_stream[j]));
+    CUDA_TRY(cudaStreamWaitEvent(stream, st.panel_done[j], 0));
+  }
+  CUDA_TRY(cudaMemcpyAsync(st.error_host, st.error_dev, sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+  CUDA_TRY(cudaStreamSynchronize(stream));
+  if (*st.error_host != 0) {
+    set_error("device-side bounded wait timed out (code %d)", *st.error_host);
+    *st.error_host = 0;
+    cudaMemsetAsync(st.error_dev, 0, sizeof(int32_t), stream);
+    cudaStreamSynchronize(stream);
+    return CPUOPS_B200_STATUS_DEVICE_TIMEOUT;
+  }
+  return CPUOPS_B200_STATUS_SUCCESS;
+}
+
 // Descriptor checks that need no device, in the CPU library's order (gemm.h:100-122,
 // gemm_mx.h:79-112).  Returns a status; *finished is set when that status is final (an
 // error, or the empty problem, which succeeds without touching anything).
@@ -486,85 +569,8 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     ch.pair = legal && want;
   }
 
-  // ---- host operands of a large problem: row panels on three streams ---------------------
-  // A call whose A and D live in host memory is bound by the PCIe copies, not by the
-  // GEMM.  Run serially (upload everything, compute, download everything) the two copy
-  // directions never overlap.  Instead: stage the B side once, then cut the output rows
-  // into panels and issue each panel as its own call (host A/C/D rows, device B) on one
-  // of three streams; a panel's upload, its neighbour's GEMM and the download of the
-  // one before overlap, and both copy engines stay busy.  Every panel uses the tile
-  // width and the single k slice chosen for the whole problem, so each element is
-  // computed exactly as the unsplit call would compute it.
-  if (depth == 0 && k > 0 && !a_dev && !d_dev && !ch.swap && ch.slices == 1 && m >= 1024) {
-    Plan bplan;
-    size_t pb = 0, psb = 0;
-    const int64_t b_pitch_staged = align_up(B.inner_bytes, 16);
-    if (!b_dev) pb = bplan.take(b_pitch_staged * B.outer);
-    if (is_mx && !sb_dev) psb = bplan.take(static_cast<size_t>(n) * d->ld_scales_b);
-    uint8_t* bw = nullptr;
-    if (bplan.total > 0) {
-      if (int rc = ensure_workspace(st, stream, bplan.total, &bw)) return rc;
-    }
-    cpuops_b200_gemm_desc sub = *d;
-    if (!b_dev) {
-      CUDA_TRY(cudaMemcpy2DAsync(bw + pb, b_pitch_staged, d->b, B.pitch, B.inner_bytes, B.outer,
-                                 cudaMemcpyHostToDevice, stream));
-      sub.b = bw + pb;
-      sub.ldb = static_cast<int32_t>(fp4_b ? b_pitch_staged * 2 : b_pitch_staged);
-    }
-    if (is_mx && !sb_dev) {
-      CUDA_TRY(cudaMemcpyAsync(bw + psb, d->b_scales,
-                               static_cast<size_t>(n - 1) * d->ld_scales_b + (k + 31) / 32,
-                               cudaMemcpyHostToDevice, stream));
-      sub.b_scales = bw + psb;
-    }
-    CUDA_TRY(cudaEventRecord(st.fork_event, stream));
-    sub.memory_space = CPUOPS_B200_MEM_AUTO;
-    sub.flags |= CPUOPS_B200_FLAG_ASYNC;
-    sub.split_k_slices = 1;
-    sub.tile_n = ch.BN;
-    int n_panels = std::max(2, std::min(8, m / 512));
-    if (env_switches().panels > 0) n_panels = std::max(2, std::min(env_switches().panels, m / 128));
-    const int panel_rows = static_cast<int>(align_up((m + n_panels - 1) / n_panels, 128));
-    int issued = 0;
-    for (int row0 = 0; row0 < m; row0 += panel_rows, ++issued) {
-      const int j = issued % DeviceState::kPanelStreams;
-      if (issued < DeviceState::kPanelStreams)
-        CUDA_TRY(cudaStreamWaitEvent(st.panel_stream[j], st.fork_event, 0));
-      cpuops_b200_gemm_desc pd = sub;
-      pd.m = std::min(panel_rows, m - row0);
-      pd.stream = st.panel_stream[j];
-      // A: k-major rows of m (row pitch A.pitch bytes), or m contiguous (int8 column-major)
-      pd.a = static_cast<const uint8_t*>(d->a) + (a_kmajor ? row0 * A.pitch : static_cast<int64_t>(row0));
-      if (is_mx)
-        pd.a_scales = static_cast<const uint8_t*>(d->a_scales) + static_cast<int64_t>(row0) * d->ld_scales_a;
-      const int64_t c_off = c_rm ? static_cast<int64_t>(row0) * d->ldc : row0;
-      const int64_t d_off = c_rm ? static_cast<int64_t>(row0) * d->ldd : row0;
-      pd.c = static_cast<const uint8_t*>(d->c) + c_off * 4;
-      pd.d = static_cast<uint8_t*>(d->d) + d_off * 4;
-      for (int t = 0; t < pd.n_ops; ++t)
-        if (pd.ops[t].opcode == CPUOPS_B200_OP_SCALE_PER_ROW)
-          pd.ops[t].ptr = static_cast<const uint8_t*>(d->ops[t].ptr) + static_cast<int64_t>(row0) * 4;
-      if (int rc = gemm_body(&pd, 1)) {
-        for (int q = 0; q < DeviceState::kPanelStreams; ++q) cudaStreamSynchronize(st.panel_stream[q]);
-        return rc;
-      }
-    }
-    for (int j = 0; j < std::min(issued, static_cast<int>(DeviceState::kPanelStreams)); ++j) {
-      CUDA_TRY(cudaEventRecord(st.panel_done[j], st.panel_stream[j]));
-      CUDA_TRY(cudaStreamWaitEvent(stream, st.panel_done[j], 0));
-    }
-    CUDA_TRY(cudaMemcpyAsync(st.error_host, st.error_dev, sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
-    CUDA_TRY(cudaStreamSynchronize(stream));
-    if (*st.error_host != 0) {
-      set_error("device-side bounded wait timed out (code %d)", *st.error_host);
-      *st.error_host = 0;
-      cudaMemsetAsync(st.error_dev, 0, sizeof(int32_t), stream);
-      cudaStreamSynchronize(stream);
-      return CPUOPS_B200_STATUS_DEVICE_TIMEOUT;
-    }
-    return CPUOPS_B200_STATUS_SUCCESS;
-  }
+  if (depth == 0 && k > 0 && !a_dev && !d_dev && !ch.swap && ch.slices == 1 && m >= 1024)
+    return run_host_row_panels(d, st, stream, ch, A, B, is_mx, fp4_b, a_kmajor, b_dev, sb_dev, c_rm);
 
   // ---- workspace plan ------------------------------------------------------------------
   Plan plan;
