@@ -20,7 +20,8 @@ def _device_args(op, P, t, D):
 
 
 @pytest.mark.parametrize("fmt,m,n,k", [(FMT_E2M1, 8, 1024, 2048), (FMT_E4M3, 1, 640, 1024),
-                                      (FMT_E4M3, 300, 500, 1024)])
+                                      (FMT_E4M3, 300, 500, 1024), (FMT_E2M1, 33, 300, 4096 + 96),
+                                      (FMT_E4M3, 64, 1792, 1000), (FMT_E2M1, 1, 14336, 4096)])
 def test_prepared_b_gives_the_same_bits(gpu, oracle, fmt, m, n, k):
     dev = torch.device("cuda", 0)
     P = W.mx_problem(fmt, m, n, k, True, seed=n + k)
@@ -37,6 +38,7 @@ def test_prepared_b_gives_the_same_bits(gpu, oracle, fmt, m, n, k):
             D1 = torch.full((P.C.size,), float("nan"), device=dev)
             assert op(_device_args(op, P, t, D1)) == c.Status.kSuccess, _capi.last_error()
             assert _capi.last_plan().prepared_b == 1
+
             # reference: the same operands with the weights not registered (other address)
             sb_copy = t["SB"].clone()
             t2 = dict(t, SB=sb_copy)
