@@ -317,6 +317,58 @@ def config_of(wl, world):
                   "twice the L2"}
 
 
+TABLE_WORKLOADS = ("int8_2048", "mxfp8_e4m3_4096", "mxfp4_decode_m1", "mxfp4_decode_m8", "mxfp4_decode_m32",
+                   "int8_8192_chain", "mx_e5m2_16384", "mx_e2m1_16384", "int8_8192", "mxfp8_8192", "mxfp4_8192")
+
+
+def run_table(args):
+    """One line per workload, in the manner of the reference's benchmark program
+    (examples/01_benchmark.cc:204-343 prints name, shape, best time and rate per config):
+    device-resident operands over rotating sets larger than the L2, best and median of `--steps` calls
+    timed one by one with CUDA events.  A survey, not the contract line."""
+    import torch
+    import cpu_ops_b200 as c
+    from cpu_ops_b200 import _capi
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks, _ = load_peaks()
+    stream = torch.cuda.current_stream().cuda_stream
+    print(f"{'workload':18s} {'m':>6s} {'n':>6s} {'k':>6s} {'plan':>14s} {'best us':>10s} {'median us':>10s} "
+          f"{'rate (best)':>16s} {'of peak':>8s}")
+    for name in TABLE_WORKLOADS:
+        wl = Workload(name)
+        host = wl.host_operands(seed=0)
+        set_bytes = sum(v.nbytes for v in host.values())
+        l2_bytes = torch.cuda.get_device_properties(dev).L2_cache_size
+        n_sets = max(2, -(-2 * l2_bytes // set_bytes) + 1)  # one trip round the ring outgrows the L2
+        sets = [{k_: torch.from_numpy(v).to(dev)
+                 for k_, v in (host if s_ == 0 else wl.host_operands(seed=s_)).items()} for s_ in range(n_sets)]
+        op = wl.operator(stream=stream, asynchronous=True, memory_space=_capi.MEM_DEVICE)
+        descs = [op.describe(wl.arguments(op, b)) for b in sets]
+        for i in range(max(4, n_sets)):
+            assert op.run(descs[i % n_sets]) == c.Status.kSuccess, _capi.last_error()
+        torch.cuda.synchronize()
+        times = []
+        for i in range(max(5, args.steps)):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            op.run(descs[i % n_sets])
+            e1.record()
+            e1.synchronize()
+            times.append(e0.elapsed_time(e1) * 1e-3)
+        times.sort()
+        best, med = times[0], times[len(times) // 2]
+        rate, unit = rate_of(wl, wl.m, best)
+        peak = float(peaks["hbm_gbs"]) if wl.bound == "hbm" else wl.peak_factor * float(peaks["bf16_tflops"])
+        plan = _capi.last_plan()
+        tile = f"{256 if plan.pair else 128}x{plan.tile_n}" + (f"/k{plan.slices}" if plan.slices > 1 else "")
+        print(f"{name:18s} {wl.m:6d} {wl.n:6d} {wl.k:6d} {tile:>14s} {best * 1e6:10.1f} {med * 1e6:10.1f} "
+              f"{rate:10.1f} {unit:>5s} {rate / peak:8.2f}")
+        del sets, descs
+        torch.cuda.empty_cache()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -327,6 +379,9 @@ def main():
     ap.add_argument("--tile-n", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--table", action="store_true",
+                    help="survey of every workload on one GPU (best / median call time), instead of the "
+                         "JSON contract line")
     ap.add_argument("--gather", action="store_true",
                     help="N > 1: every step also all-gathers the ranks' D row blocks into a replicated D "
                          "(NCCL, on a second stream so that it overlaps the next step's GEMM)")
@@ -346,6 +401,8 @@ def main():
 
     if args.impl == "reference":
         return run_reference_arm(args, wl, rank, world)
+    if args.table:
+        return run_table(args)
 
     import torch
     import torch.distributed as dist
