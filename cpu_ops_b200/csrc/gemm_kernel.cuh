@@ -190,19 +190,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       reinterpret_cast<uint32_t*>(smem + (bar_base - smem_base) + 8 * (2 * kMaxStages + 5 + 8));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < stages; ++s) {
-      mbar_init(full_bar(s), 1);   // producer's arrive.expect_tx
-      mbar_init(empty_bar(s), 1);  // tcgen05.commit of the MMAs that read the stage
+  // Barrier initialisation, one barrier per lane of warp 2 (indices as laid out above:
+  // 0-7 full, 8-15 empty, 16-17 accumulator full, 18-19 accumulator empty, 20 drain,
+  // 21-28 C chunks), while warp 1 allocates tensor memory and warp 0 fetches descriptors.
+  if (warp == 2) {
+    constexpr int kBarriers = 2 * kMaxStages + 5 + 8;
+    if (lane < kBarriers) {
+      // full: the producer's arrive.expect_tx; empty / accumulator full / drain: one
+      // tcgen05.commit; accumulator empty: one arrival per epilogue warp (of both CTAs);
+      // C chunk: the TMA load's expect_tx
+      const bool acc_empty = lane == 2 * kMaxStages + 2 || lane == 2 * kMaxStages + 3;
+      mbar_init(bar_base + 8u * static_cast<uint32_t>(lane), acc_empty ? 4u * kCtas : 1u);
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(acc_full_bar(b), 1);   // tcgen05.commit after the tile's last MMA
-      mbar_init(acc_empty_bar(b), 4 * kCtas);  // one arrival per epilogue warp (of both CTAs)
-    }
-    mbar_init(drain_bar, 1);
-    for (int w = 0; w < 4; ++w)
-      for (int b = 0; b < 2; ++b) mbar_init(c_full_bar(w, b), 1);  // TMA load of one C chunk
-    *abort_flag = 0;
+    if (lane == 0) *abort_flag = 0;
     if constexpr (kPair) {
       fence_mbar_init_cluster();
     } else {
@@ -216,6 +216,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   if (warp == 0 && lane == 0) {
     prefetch_tensormap(&tmA);
     prefetch_tensormap(&tmB);
+    if (p.c_ring) prefetch_tensormap(&tmC);
+    if (p.d_tma) prefetch_tensormap(&tmD);
+    if constexpr (kMx && kPair) {
+      prefetch_tensormap(&tmSFA);
+      prefetch_tensormap(&tmSFB);
+    }
   }
   tc_fence_before_sync();
   if constexpr (kPair) {
