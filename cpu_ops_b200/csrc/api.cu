@@ -918,6 +918,8 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
       p.d_tma = 1;
     }
     p.ring_bufs = (p.c_ring || p.d_tma) ? 2 : 0;
+    if (p.ring_bufs && env_switches().ring == 3) p.ring_bufs = 3;
+    const int epi_warps = env_switches().epi_warps == 8 ? 8 : 4;
     p.error = st.error_dev;
     p.debug_flags = env_switches().debug_flags;
     if (env_switches().clk) {
@@ -928,7 +930,7 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     }
     const int sf_stage_bytes = p.sfa_stage_bytes + p.sfb_stage_bytes;
     const int per_stage = gemm_stage_bytes(b_rows) + sf_stage_bytes;
-    int stages = (st.smem_optin - 1024 - kBarrierBytes - (p.ring_bufs ? 1024 + ring_bytes(p.ring_bufs) : 0)) /
+    int stages = (st.smem_optin - 1024 - kBarrierBytes - (p.ring_bufs ? 1024 + ring_bytes(p.ring_bufs, epi_warps) : 0)) /
                  per_stage;
     stages = std::min({stages, kMaxStages, std::max(2, k_blocks)});
     if (stages < 2) {
@@ -937,13 +939,13 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     }
     p.stages = stages;
     // At least 120 KB so that two CTAs never share an SM: each allocates all of tensor memory.
-    const int smem = std::max(gemm_smem_bytes(b_rows, stages, sf_stage_bytes, p.ring_bufs),
+    const int smem = std::max(gemm_smem_bytes(b_rows, stages, sf_stage_bytes, p.ring_bufs, epi_warps),
                               120 * 1024);
     const int64_t total_tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles * p.slices;
     unsigned grid = static_cast<unsigned>(std::min<int64_t>(total_tiles, st.sm_count));
     CUtensorMap tmSFA = tmA, tmSFB = tmA;  // used by the pair kernel's scale loads only
     cudaLaunchConfig_t cfg = {};
-    cfg.blockDim = dim3(kGemmThreads);
+    cfg.blockDim = dim3(epi_warps == 8 ? kGemmThreadsWide : kGemmThreads);
     cfg.dynamicSmemBytes = static_cast<size_t>(smem);
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];

@@ -30,7 +30,8 @@
 
 namespace b200 {
 
-constexpr int kGemmThreads = 192;  // producer, MMA issuer, 4 epilogue warps
+constexpr int kGemmThreads = 192;      // producer, MMA issuer, 4 epilogue warps
+constexpr int kGemmThreadsWide = 320;  // ... or 8 epilogue warps, two per TMEM lane quarter
 constexpr uint32_t kTmemCols = 512;
 
 struct TileCoord {
@@ -72,12 +73,13 @@ __device__ __forceinline__ bool aligned16(const void* ptr) {
 }
 
 // Stores one 32-column chunk of one accumulator row.
-// `c_smem_row`: this thread's row of the C chunk prefetched into the ring, or null.
-// `d_smem_row`: where to put the finished row for the TMA store, or null (store directly).
+// `c_smem_row`: shared-memory address of this thread's row of the C chunk prefetched into
+// the ring, or 0.  `d_smem_row`: where to put the finished row for the TMA store, or 0
+// (store directly).  Explicit shared-space accesses: generic ones cost more.
 template <bool kInt>
 __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[32], int krow,
-                                            int kcol0, int slice, const uint32_t* c_smem_row,
-                                            uint32_t* d_smem_row, int c_swz) {
+                                            int kcol0, int slice, uint32_t c_smem_row,
+                                            uint32_t d_smem_row, int c_swz) {
   const int ncols = min(32, p.Nk - kcol0);
   if (p.mode == kModePartial) {
     uint32_t* w = static_cast<uint32_t*>(p.ws) + (slice * p.ws_slab + krow * p.ws_sr + kcol0 * p.ws_sc);
@@ -94,13 +96,13 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[3
   }
   const EpilogueParams& e = p.epi;
   uint32_t src[32];
-  if (c_smem_row != nullptr) {
+  if (c_smem_row != 0) {
     // C chunk prefetched by TMA: this thread's row, 16-byte pieces XOR-swizzled by row & 7
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const uint4 v = *reinterpret_cast<const uint4*>(c_smem_row + ((j ^ c_swz) << 2));
-      src[4 * j] = v.x; src[4 * j + 1] = v.y; src[4 * j + 2] = v.z; src[4 * j + 3] = v.w;
-    }
+    for (int j = 0; j < 8; ++j)
+      asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(src[4 * j]), "=r"(src[4 * j + 1]), "=r"(src[4 * j + 2]), "=r"(src[4 * j + 3])
+                   : "r"(c_smem_row + (static_cast<uint32_t>(j ^ c_swz) << 4)));
   } else if (e.beta_nonzero) {
     // plain loads: C may alias D
     const uint32_t* c = static_cast<const uint32_t*>(e.C) + (krow * e.c_sr + kcol0 * e.c_sc);
@@ -121,12 +123,14 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[3
 #pragma unroll
   for (int i = 0; i < 32; ++i) r[i] = linear_combine_bits<kInt>(e, r[i], src[i]);
   for (int t = 0; t < e.n_ops; ++t) apply_op_chunk<kInt>(e.ops[t], r, krow, kcol0, ncols);
-  if (d_smem_row != nullptr) {
+  if (d_smem_row != 0) {
     // same 16-byte-piece swizzle as the TMA box (row & 7)
 #pragma unroll
     for (int j = 0; j < 8; ++j)
-      *reinterpret_cast<uint4*>(d_smem_row + ((j ^ c_swz) << 2)) =
-          make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+      asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(
+                       d_smem_row + (static_cast<uint32_t>(j ^ c_swz) << 4)),
+                   "r"(r[4 * j]), "r"(r[4 * j + 1]), "r"(r[4 * j + 2]), "r"(r[4 * j + 3])
+                   : "memory");
     return;
   }
   uint32_t* d = static_cast<uint32_t*>(e.D) + (krow * e.d_sr + kcol0 * e.d_sc);
@@ -148,7 +152,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t (&r)[3
 // stage in both CTAs with a multicast commit, and each CTA's epilogue warps drain their
 // own 128 accumulator rows.  p.m_tiles counts 256-row tiles in that case.
 template <int KIND, bool kPair>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemmThreadsWide, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                         const __grid_constant__ CUtensorMap tmB,
                         const __grid_constant__ CUtensorMap tmC,
@@ -179,28 +183,33 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const uint32_t sf_base = smem_base + stages * stage_bytes;
   // Optional ring of C chunks (32 rows x 32 columns, 128-byte swizzled), two per epilogue warp.
   const uint32_t c_base = (sf_base + stages * sf_stage + 1023u) & ~1023u;
-  const uint32_t bar_base = p.ring_bufs ? c_base + ring_bytes(p.ring_bufs) : sf_base + stages * sf_stage;
+  // Epilogue warps: 4, or 8 when launched with kGemmThreadsWide threads (two per TMEM lane
+  // quarter, which take alternate 32-column chunks of the tile).
+  const int n_epi = static_cast<int>(blockDim.x >> 5) - 2;
+  const uint32_t bar_base =
+      p.ring_bufs ? c_base + ring_bytes(p.ring_bufs, n_epi) : sf_base + stages * sf_stage;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
   auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * kMaxStages + b); };
   auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * kMaxStages + 2 + b); };
   const uint32_t drain_bar = bar_base + 8u * (2 * kMaxStages + 4);
-  auto c_full_bar = [&](int w, int b) { return bar_base + 8u * (2 * kMaxStages + 5 + w * 2 + b); };
-  uint32_t* tmem_slot =
-      reinterpret_cast<uint32_t*>(smem + (bar_base - smem_base) + 8 * (2 * kMaxStages + 5 + 8));
+  auto c_full_bar = [&](int w, int b) { return bar_base + 8u * (2 * kMaxStages + 5 + w * 3 + b); };
+  constexpr int kBarriers = 2 * kMaxStages + 5 + 24;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + (bar_base - smem_base) + 8 * kBarriers);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   // Barrier initialisation, one barrier per lane of warp 2 (indices as laid out above:
   // 0-7 full, 8-15 empty, 16-17 accumulator full, 18-19 accumulator empty, 20 drain,
-  // 21-28 C chunks), while warp 1 allocates tensor memory and warp 0 fetches descriptors.
+  // 21-44 C chunks: up to three per epilogue warp), while warp 1 allocates tensor memory
+  // and warp 0 fetches descriptors.
   if (warp == 2) {
-    constexpr int kBarriers = 2 * kMaxStages + 5 + 8;
-    if (lane < kBarriers) {
+    for (int i = lane; i < kBarriers; i += 32) {
       // full: the producer's arrive.expect_tx; empty / accumulator full / drain: one
       // tcgen05.commit; accumulator empty: one arrival per epilogue warp (of both CTAs);
       // C chunk: the TMA load's expect_tx
-      const bool acc_empty = lane == 2 * kMaxStages + 2 || lane == 2 * kMaxStages + 3;
-      mbar_init(bar_base + 8u * static_cast<uint32_t>(lane), acc_empty ? 4u * kCtas : 1u);
+      const bool acc_empty = i == 2 * kMaxStages + 2 || i == 2 * kMaxStages + 3;
+      mbar_init(bar_base + 8u * static_cast<uint32_t>(i),
+                acc_empty ? static_cast<uint32_t>(n_epi) * kCtas : 1u);
     }
     if (lane == 0) *abort_flag = 0;
     if constexpr (kPair) {
@@ -512,7 +521,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     __syncwarp();
   } else {
     // -------------------------------- epilogue --------------------------------
-    const int q = warp & 3;  // the TMEM lane quarter this warp can read
+    const int q = warp & 3;   // the TMEM lane quarter this warp can read
+    const int ew = warp - 2;  // index among the epilogue warps: its ring and its C barriers
+    // with 8 epilogue warps the two of a quarter take alternate chunks: c0, c0 + cstep, ...
+    const int cstep = n_epi >> 2, c0 = ew >> 2;
     int it = 0;
     const int nchunks = p.BN / 32;
     // Ring of two 4 KB chunk buffers per warp (32 rows x 32 words, 128-byte swizzled);
@@ -520,11 +532,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     // chunks ahead of their use; with d_tma, the finished chunk is written into its
     // buffer (in place over C) and leaves by TMA store, so D is written in whole 128-byte
     // row pieces; a buffer is refilled only after the store that read it is done with it.
-    // (A third buffer would hide that wait but costs a pipeline stage: measured slower.)
+    // A third buffer (p.ring_bufs == 3) hides that wait at the price of shared memory.
     const bool ring = p.c_ring != 0, d_tma = p.d_tma != 0;
     const uint32_t nb = static_cast<uint32_t>(p.ring_bufs);
-    const uint32_t my_c = c_base + static_cast<uint32_t>(q) * nb * 4096u;
-    uint8_t* my_c_ptr = smem + (my_c - smem_base);
+    const uint32_t my_c = c_base + static_cast<uint32_t>(ew) * nb * 4096u;
     uint32_t cq = 0;        // chunks consumed so far by this warp
     uint32_t cq_b = 0, cq_ph = 0;  // its buffer and that buffer's barrier parity
     uint32_t cissued = 0, ci_b = 0;  // C chunks requested so far, buffer of the next request
@@ -535,8 +546,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     // pair: the leader's MMA thread waits for the epilogue warps of both CTAs
     const uint32_t acc_empty0 = kPair ? map_to_cta(acc_empty_bar(0), 0) : acc_empty_bar(0);
     auto request_c = [&](int col, int row) {  // lane 0 only
-      mbar_expect_tx(c_full_bar(q, ci_b), 4096u);
-      tma_load_2d(my_c + ci_b * 4096u, &tmC, c_full_bar(q, ci_b), col, row);
+      mbar_expect_tx(c_full_bar(ew, ci_b), 4096u);
+      tma_load_2d(my_c + ci_b * 4096u, &tmC, c_full_bar(ew, ci_b), col, row);
       ++cissued;
       if (++ci_b == nb) ci_b = 0;
     };
@@ -548,9 +559,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const int krow = row0 + lane;
       const int n0 = tc.n_tile * p.BN;
       if (ring && lane == 0) {
-        // first two chunks of this tile: requested before the accumulator is ready
+        // this warp's first two chunks of the tile: requested before the accumulator is ready
         if (d_tma) bulk_wait_group_read<0>();
-        for (int c = 0; c < 2 && c < nchunks; ++c) request_c(n0 + c * 32, row0);
+        for (int c = c0; c < c0 + 2 * cstep && c < nchunks; c += cstep) request_c(n0 + c * 32, row0);
       }
       const long long te0 = edbg ? clock64() : 0;
       const bool ready = mbar_wait_bounded(acc_full_bar(buf), acc_ph, abort_flag);
@@ -563,11 +574,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                              static_cast<uint32_t>(buf * p.BN);
-      for (int c = 0; c < nchunks; ++c) {
+      if (c0 >= nchunks) {
+        // a tile narrower than this warp's first chunk: nothing to read, hand it back
+        tc_fence_before_sync();
+        if (lane == 0) {
+          if constexpr (kPair) {
+            mbar_arrive_cluster(acc_empty0 + 8u * buf);
+          } else {
+            mbar_arrive(acc_empty_bar(buf));
+          }
+        }
+      }
+      for (int c = c0; c < nchunks; c += cstep) {
         uint32_t r[32];
         tmem_ld_32x32(taddr + static_cast<uint32_t>(c * 32), r);
         tmem_ld_wait();
-        if (c == nchunks - 1) {
+        if (c + cstep >= nchunks) {
           // the accumulator is in registers: hand the buffer back to the MMA warp
           tc_fence_before_sync();
           __syncwarp();
@@ -580,22 +602,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
         }
         const int kcol0 = n0 + c * 32;
-        const uint32_t* c_row = nullptr;
-        uint32_t* d_row = nullptr;
+        uint32_t c_row = 0, d_row = 0;  // shared-memory addresses of this lane's row
         if (ring) {
-          const bool got = mbar_wait_bounded(c_full_bar(q, cq_b), cq_ph, abort_flag);
+          const bool got = mbar_wait_bounded(c_full_bar(ew, cq_b), cq_ph, abort_flag);
           if (!__all_sync(0xffffffffu, got)) {
             if (lane == 0) record_error(p, abort_flag, kErrEpilogueWait);
             alive = false;
             break;
           }
-          c_row = reinterpret_cast<const uint32_t*>(my_c_ptr + cq_b * 4096u + lane * 128);
+          c_row = my_c + cq_b * 4096u + static_cast<uint32_t>(lane) * 128u;
         } else if (d_tma) {
-          // the store that last read this buffer (two chunks ago) must be done with it
-          if (lane == 0) bulk_wait_group_read<1>();
+          // the store that last read this buffer (nb chunks ago) must be done with it
+          if (lane == 0) {
+            if (nb >= 3) bulk_wait_group_read<2>(); else bulk_wait_group_read<1>();
+          }
           __syncwarp();
         }
-        if (d_tma) d_row = reinterpret_cast<uint32_t*>(my_c_ptr + cq_b * 4096u + lane * 128);
+        if (d_tma) d_row = my_c + cq_b * 4096u + static_cast<uint32_t>(lane) * 128u;
         if (krow < p.Mk && kcol0 < p.Nk && !(p.debug_flags & 4))
           store_chunk<kInt>(p, r, krow, kcol0, tc.slice, c_row, d_row, lane & 7);
         if (d_tma) {
@@ -608,11 +631,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         } else if (ring) {
           __syncwarp();  // every lane has read its row: the buffer may be refilled
         }
-        if (ring && lane == 0 && c + 2 < nchunks) {
-          // chunk c + 2 goes where chunk c - 1 (three buffers) or chunk c (two) was
-          // chunk c + 2 reuses chunk c's buffer: its store must have read it first
-          if (d_tma) bulk_wait_group_read<0>();
-          request_c(n0 + (c + 2) * 32, row0);
+        if (ring && lane == 0 && c + 2 * cstep < nchunks) {
+          // chunk c + 2 goes where chunk c (two buffers) or chunk c - 1 (three) was: the
+          // store out of that buffer must have read it first.  With three buffers that is
+          // the store before the one just issued, which has normally finished by now.
+          if (d_tma) {
+            if (nb >= 3) bulk_wait_group_read<1>(); else bulk_wait_group_read<0>();
+          }
+          request_c(n0 + (c + 2 * cstep) * 32, row0);
         }
         ++cq;
         if (++cq_b == nb) {
@@ -630,7 +656,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       // let C chunks that were requested but never consumed land before the CTA exits
       int dummy = 0;
       for (; cq < cissued; ++cq) {
-        mbar_wait_bounded(c_full_bar(q, cq_b), cq_ph, &dummy);
+        mbar_wait_bounded(c_full_bar(ew, cq_b), cq_ph, &dummy);
         if (++cq_b == nb) {
           cq_b = 0;
           cq_ph ^= 1u;

@@ -86,11 +86,12 @@ struct GemmParams {
 // Shared-memory footprint of one launch of the GEMM kernel.
 __host__ __device__ inline int gemm_stage_bytes(int BN) { return kTileM * 128 + BN * 128; }
 // Epilogue ring: per epilogue warp `bufs` buffers of one 32 x 32-word chunk (4 KB).
-__host__ __device__ inline int ring_bytes(int bufs) { return 4 /*epilogue warps*/ * bufs * 4096; }
+__host__ __device__ inline int ring_bytes(int bufs, int epi_warps = 4) { return epi_warps * bufs * 4096; }
 constexpr int kBarrierBytes = 512;  // barriers, TMEM slot, abort flag
-__host__ __device__ inline int gemm_smem_bytes(int BN, int stages, int sf_stage_bytes, int ring_bufs = 0) {
+__host__ __device__ inline int gemm_smem_bytes(int BN, int stages, int sf_stage_bytes, int ring_bufs = 0,
+                                               int epi_warps = 4) {
   return 1024 /*alignment slack*/ + stages * (gemm_stage_bytes(BN) + sf_stage_bytes) +
-         (ring_bufs ? 1024 + ring_bytes(ring_bufs) : 0) + kBarrierBytes;
+         (ring_bufs ? 1024 + ring_bytes(ring_bufs, epi_warps) : 0) + kBarrierBytes;
 }
 
 }  // namespace b200

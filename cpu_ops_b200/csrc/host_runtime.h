@@ -221,6 +221,8 @@ struct EnvSwitches {
   int debug_flags = getenv("CPUOPS_B200_DEBUG") ? atoi(getenv("CPUOPS_B200_DEBUG")) : 0;
   int raster_m = getenv("CPUOPS_B200_RASTER") ? atoi(getenv("CPUOPS_B200_RASTER")) : 0;
   int pair = getenv("CPUOPS_B200_PAIR") ? atoi(getenv("CPUOPS_B200_PAIR")) : -1;  // -1: heuristic
+  int ring = getenv("CPUOPS_B200_RING") ? atoi(getenv("CPUOPS_B200_RING")) : 0;    // 0: heuristic
+  int epi_warps = getenv("CPUOPS_B200_EPI_WARPS") ? atoi(getenv("CPUOPS_B200_EPI_WARPS")) : 0;
 };
 const EnvSwitches& env_switches() {
   static const EnvSwitches e;
