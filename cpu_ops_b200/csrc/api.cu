@@ -72,13 +72,56 @@ int pick_bn_for_small(int nk) {
 // (about 64 bytes per clock per SM) rather than by the MMA itself (BN / 2 clocks per
 // 32-byte k step), so a k-block costs 2 * (128 + BN) clocks; the epilogue overlaps
 // the next tile's k loop only when there are two accumulator buffers.
-double config_cost(int Mk, int Nk, int k_blocks, int BN, int nacc, int sms, bool beta) {
-  const int64_t tiles = static_cast<int64_t>((Mk + 127) / 128) * ((Nk + BN - 1) / BN);
-  const int64_t waves = (tiles + sms - 1) / sms;
-  const double kblock = std::max(2.0 * BN, 2.0 * (128.0 + BN));
-  const double epi = 128.0 * BN * (beta ? 8.0 : 4.0) / 20.0;  // ~20 B/clk/SM of HBM
-  const double tile = k_blocks * kblock + (nacc == 1 ? epi : 0.15 * epi);
-  return static_cast<double>(waves) * tile;
+// Whether a launch runs as pairs of CTAs on 256-row tiles (see gemm_body).
+bool pair_pays(int Mk, int Nk, int k_blocks, int BN, int slices, int sms, bool bk_role_mn) {
+  const int64_t tiles = static_cast<int64_t>((Mk + 127) / 128) * ((Nk + BN - 1) / BN) * slices;
+  const bool legal = Mk > 128 && (!bk_role_mn || BN == 256) && BN % 32 == 0;
+  return legal && tiles >= 2 * sms && k_blocks >= 8;
+}
+
+// Estimated SM cycles of an unsplit launch with tile width BN.  Per k-block a CTA is bound
+// by the L2 -> shared-memory feed (about 64 bytes per cycle: 128 rows of A plus its rows of
+// B, 128 bytes each) or by the MMAs (BN / 2 cycles per 32-byte k step); the epilogue hides
+// behind the next tile's k loop when there are two accumulators.  The tiles are dealt to
+// the workers (CTAs or pairs) round-robin, and a ragged last tile column is cheaper when it
+// can be computed at its own width (slot_to_tile), so the cost is the busiest worker's.
+double config_cost(int Mk, int Nk, int k_blocks, int BN, int nacc, int sms, bool beta, bool bk_role_mn) {
+  const bool pair = pair_pays(Mk, Nk, k_blocks, BN, 1, sms, bk_role_mn);
+  const int tile_m = pair ? 256 : 128;
+  const int m_tiles = (Mk + tile_m - 1) / tile_m, n_tiles = (Nk + BN - 1) / BN;
+  const int workers = std::max(1, pair ? sms / 2 : sms);
+  auto tile_cost = [&](int width) {
+    const double b_rows = pair ? width / 2.0 : width;
+    const double kblock = std::max(2.0 * width, 2.0 * (128.0 + b_rows));
+    const double epi = 128.0 * width * (beta ? 8.0 : 4.0) / 20.0;  // ~20 B/clk/SM of HBM
+    return k_blocks * kblock + (nacc == 1 ? epi : 0.15 * epi);
+  };
+  const int last = last_tile_width(Nk, BN);
+  const bool narrow_last = !bk_role_mn && n_tiles >= 2 && last < BN;
+  const int narrow = narrow_last ? m_tiles : 0, wide = m_tiles * n_tiles - narrow;
+  const double cw = tile_cost(BN), cn = narrow_last ? tile_cost(last) : cw;
+  const int64_t total = static_cast<int64_t>(wide) + narrow;
+  if (total > 64ll * workers) return (wide * cw + narrow * cn) / workers + cw;  // rounding is noise
+  std::vector<double> load(static_cast<size_t>(workers), 0.0);
+  for (int v = 0; v < total; ++v)
+    load[static_cast<size_t>(v % workers)] += slot_to_tile(v, wide, narrow, workers).narrow ? cn : cw;
+  return *std::max_element(load.begin(), load.end());
+}
+
+// Tile width for a kernel-view n extent above 128: the cheapest of the candidates.
+int pick_tile_width(int Mk, int Nk, int k_blocks, bool is_mx, int sms, bool beta, bool bk_role_mn) {
+  double best = 1e300;
+  int width = 128;
+  for (int bn : {256, 224, 192, 160, 128}) {
+    if (bk_role_mn && bn % 128 != 0) continue;
+    const int nacc = (is_mx && bn > 224) ? 1 : 2;  // MX: the scale slots need tensor-memory columns too
+    const double c = config_cost(Mk, Nk, k_blocks, bn, nacc, sms, beta, bk_role_mn);
+    if (c < best) {
+      best = c;
+      width = bn;
+    }
+  }
+  return width;
 }
 
 }  // namespace
@@ -133,6 +176,22 @@ CPUOPS_B200_API int cpuops_b200_release_b(void* handle) {
   }
   set_error("release_b: unknown handle");
   return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+}
+
+// Undeclared (tests only): the work order of a launch with a narrow last tile column.
+CPUOPS_B200_API int cpuops_b200_debug_slot_to_tile(int32_t v, int32_t wide, int32_t narrow, int32_t workers,
+                                                   int32_t* is_narrow, int32_t* index) {
+  if (!is_narrow || !index || workers <= 0 || wide < 0 || narrow < 0 || v < 0 || v >= wide + narrow) return 1;
+  const SlotTile t = slot_to_tile(v, wide, narrow, workers);
+  *is_narrow = t.narrow;
+  *index = t.index;
+  return 0;
+}
+
+// Undeclared (tests only): the tile width the launcher picks for a kernel-view problem.
+CPUOPS_B200_API int cpuops_b200_debug_pick_tile_width(int32_t Mk, int32_t Nk, int32_t k_blocks, int32_t is_mx,
+                                                      int32_t sms, int32_t beta, int32_t n_contiguous_b) {
+  return pick_tile_width(Mk, Nk, k_blocks, is_mx != 0, sms, beta != 0, n_contiguous_b != 0);
 }
 
 CPUOPS_B200_API int cpuops_b200_last_plan(cpuops_b200_plan* out) {
@@ -513,16 +572,7 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     } else if (Nk <= 128) {
       ch.BN = bk_role_mn ? 128 : pick_bn_for_small(Nk);
     } else {
-      double best = 1e300;
-      for (int bn : {256, 224, 192, 160, 128}) {
-        if (bk_role_mn && bn % 128 != 0) continue;
-        const int nacc = (is_mx && bn > 224) ? 1 : 2;
-        const double c = config_cost(Mk, Nk, k_blocks, bn, nacc, st.sm_count, beta_nonzero);
-        if (c < best) {
-          best = c;
-          ch.BN = bn;
-        }
-      }
+      ch.BN = pick_tile_width(Mk, Nk, k_blocks, is_mx, st.sm_count, beta_nonzero, bk_role_mn);
     }
     if (ch.BN % 32 != 0 || ch.BN < 32 || ch.BN > 256 || (bk_role_mn && ch.BN % 128 != 0)) {
       set_error("tile_n %d is not usable here", ch.BN);
@@ -561,8 +611,7 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     const int Mk = ch.swap ? n : m, Nk = ch.swap ? m : n;
     const bool bk_role_mn = !(ch.swap ? a_kmajor : b_kmajor);
     const bool legal = Mk > 128 && (!bk_role_mn || ch.BN == 256) && ch.BN % 32 == 0;
-    const int64_t tiles = static_cast<int64_t>((Mk + 127) / 128) * ((Nk + ch.BN - 1) / ch.BN) * ch.slices;
-    bool want = tiles >= 2 * st.sm_count && k_blocks >= 8;
+    bool want = pair_pays(Mk, Nk, k_blocks, ch.BN, ch.slices, st.sm_count, bk_role_mn);
     if (env_switches().pair >= 0) want = env_switches().pair != 0;
     if (d->flags & CPUOPS_B200_FLAG_PAIR_ON) want = true;
     if (d->flags & CPUOPS_B200_FLAG_PAIR_OFF) want = false;
@@ -865,6 +914,13 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     }
     p.a_mn_major = ak_kmajor ? 0 : 1;
     p.b_mn_major = bk_kmajor ? 0 : 1;
+    // A ragged last tile column is computed at its own width (k-contiguous B only: an
+    // n-contiguous B tile is staged in fixed 128-column pieces) and its cheaper tiles are
+    // dealt to the work slots that would otherwise end a whole tile late.
+    p.narrow_last = (p.slices == 1 && p.n_tiles >= 2 && bk_kmajor && last_tile_width(Nk, ch.BN) < ch.BN &&
+                     !env_switches().no_narrow)
+                        ? 1
+                        : 0;
     if (!is_mx) {
       // A side is u8 unless the operands were swapped (then it is the caller's s8 B)
       const uint32_t a_fmt = swap ? 1u : 0u, b_fmt = swap ? 0u : 1u;

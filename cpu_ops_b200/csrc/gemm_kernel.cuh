@@ -36,6 +36,7 @@ constexpr uint32_t kTmemCols = 512;
 
 struct TileCoord {
   int m_tile, n_tile, slice, kb0, nkb;
+  int bn;  // width this tile is computed at: p.BN, or less for a narrow last column
 };
 
 // Work item -> (m tile, n tile, k slice).  Tiles are walked in groups of
@@ -43,18 +44,36 @@ struct TileCoord {
 // band of A and a band of B of about the same size in L2.  k-slices are balanced contiguous
 // ranges of 128-byte k-blocks, like the CPU library's split_range
 // (gemm/threadblock/threadblock_swizzle.h:31-37).
-__device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int t) {
+// With p.narrow_last (unsplit launches only) the last tile column is computed at its own
+// width and its tiles are dealt to the work slots by slot_to_tile; `workers` is the
+// number of CTAs (pairs) that share the work items round-robin.
+__device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int t, int workers) {
   TileCoord c;
   const int mn = p.m_tiles * p.n_tiles;
   c.slice = t / mn;
-  const int r = t - c.slice * mn;
-  const int per_group = p.raster_m * p.n_tiles;
-  const int g = r / per_group;
-  const int first_m = g * p.raster_m;
-  const int gsize = min(p.raster_m, p.m_tiles - first_m);
-  const int in = r - g * per_group;
-  c.m_tile = first_m + in % gsize;
-  c.n_tile = in / gsize;
+  int r = t - c.slice * mn;
+  int n_cols = p.n_tiles;  // tile columns walked in raster order
+  c.bn = p.BN;
+  bool narrow = false;
+  if (p.narrow_last) {
+    n_cols = p.n_tiles - 1;
+    const SlotTile st = slot_to_tile(r, p.m_tiles * n_cols, p.m_tiles, workers);
+    narrow = st.narrow != 0;
+    r = st.index;
+  }
+  if (narrow) {
+    c.m_tile = r;
+    c.n_tile = p.n_tiles - 1;
+    c.bn = last_tile_width(p.Nk, p.BN);
+  } else {
+    const int per_group = p.raster_m * n_cols;
+    const int g = r / per_group;
+    const int first_m = g * p.raster_m;
+    const int gsize = min(p.raster_m, p.m_tiles - first_m);
+    const int in = r - g * per_group;
+    c.m_tile = first_m + in % gsize;
+    c.n_tile = in / gsize;
+  }
   const int base = p.k_blocks / p.slices, rem = p.k_blocks % p.slices;
   c.kb0 = c.slice * base + min(c.slice, rem);
   c.nkb = base + (c.slice < rem ? 1 : 0);
@@ -289,10 +308,11 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
       long long pdbg_wait = 0;
       const long long pdbg_start = pdbg ? clock64() : 0;
       for (int t = work0; t < total_tiles && ok; t += work_step) {
-        const TileCoord tc = decode_tile(p, t);
+        const TileCoord tc = decode_tile(p, t, work_step);
         const int m_tile128 = tc.m_tile * kCtas + static_cast<int>(cta_rank);  // this CTA's 128 rows
         const int m0 = m_tile128 * kTileM;
-        const int n0 = tc.n_tile * p.BN + static_cast<int>(cta_rank) * b_rows;  // this CTA's B rows
+        // this CTA's B rows: its half of the width the tile is computed at
+        const int n0 = tc.n_tile * p.BN + static_cast<int>(cta_rank) * (tc.bn / kCtas);
         int kx = tc.kb0 * 128;  // k coordinate (bytes along k) of the next block
         const uint8_t* sfa_base = nullptr;  // this tile's scale atoms, k-block 0
         const uint8_t* sfb_base = nullptr;
@@ -403,16 +423,20 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
       const uint32_t stage_step = static_cast<uint32_t>(stage_bytes) >> 4;
       const uint32_t a_k = p.a_mn_major ? 256u : 2u;  // descriptor step per 32-byte k step
       const uint32_t b_k = p.b_mn_major ? 256u : 2u;
-      const uint32_t idesc = p.idesc;
-      uint32_t id1 = idesc, id2 = idesc, id3 = idesc;
-      if constexpr (KIND == kKindMxf8) {  // one scale byte per MMA: byte j of the column
-        id1 = idesc_with_sf_ids(idesc, 1, 1);
-        id2 = idesc_with_sf_ids(idesc, 2, 2);
-        id3 = idesc_with_sf_ids(idesc, 3, 3);
-      } else if constexpr (KIND == kKindMxf4) {  // two scale bytes per MMA: half-word j & 1
-        id1 = idesc_with_sf_ids(idesc, 2, 2);
-        id3 = id1;
-      }
+      uint32_t idesc = p.idesc, id1 = idesc, id2 = idesc, id3 = idesc;
+      auto set_idesc_width = [&](int bn) {  // N field [17,23) = width >> 3
+        idesc = (p.idesc & ~(0x3Fu << 17)) | (static_cast<uint32_t>(bn >> 3) << 17);
+        id1 = id2 = id3 = idesc;
+        if constexpr (KIND == kKindMxf8) {  // one scale byte per MMA: byte j of the column
+          id1 = idesc_with_sf_ids(idesc, 1, 1);
+          id2 = idesc_with_sf_ids(idesc, 2, 2);
+          id3 = idesc_with_sf_ids(idesc, 3, 3);
+        } else if constexpr (KIND == kKindMxf4) {  // two scale bytes per MMA: half-word j & 1
+          id1 = idesc_with_sf_ids(idesc, 2, 2);
+          id3 = id1;
+        }
+      };
+      set_idesc_width(p.BN);
       const uint32_t sf_t0 = tmem_base + sf_col0;
       uint32_t sfa_t = sf_t0, sf_q = 0;
       const uint32_t sf_hi = static_cast<uint32_t>(sf_hi64 >> 32);
@@ -428,7 +452,7 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
       uint32_t ph = 0, acc_ph = 0, peek = 0;
       uint32_t a_lo = a_lo0, b_lo = b_lo0, full_addr = full0, empty_addr = empty0, sf_lo = sf_lo0;
       for (int t = work0; t < total_tiles && ok; t += work_step) {
-        const TileCoord tc = decode_tile(p, t);
+        const TileCoord tc = decode_tile(p, t, work_step);
         long long tw0 = dbg ? clock64() : 0;
         if (!__all_sync(kAll, mbar_wait_bounded(acc_empty_bar(buf), acc_ph ^ 1u, abort_flag))) {
           if (el) record_error(p, abort_flag, kErrMmaWaitAcc);
@@ -437,6 +461,7 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
         if (dbg) dbg_wait_acc += clock64() - tw0;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * p.BN);
+        if (p.narrow_last) set_idesc_width(tc.bn);
         uint32_t accumulate = 0;
         for (int i = 0; i < tc.nkb; ++i) {
           tw0 = dbg ? clock64() : 0;
@@ -526,7 +551,6 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
     // with 8 epilogue warps the two of a quarter take alternate chunks: c0, c0 + cstep, ...
     const int cstep = n_epi >> 2, c0 = ew >> 2;
     int it = 0;
-    const int nchunks = p.BN / 32;
     // Ring of two 4 KB chunk buffers per warp (32 rows x 32 words, 128-byte swizzled);
     // chunk x uses buffer x % 2.  With c_ring, C chunks are fetched into it by TMA two
     // chunks ahead of their use; with d_tma, the finished chunk is written into its
@@ -552,12 +576,13 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
       if (++ci_b == nb) ci_b = 0;
     };
     for (int t = work0; t < total_tiles && alive; t += work_step, ++it) {
-      const TileCoord tc = decode_tile(p, t);
+      const TileCoord tc = decode_tile(p, t, work_step);
       const int buf = it % nacc;
       const uint32_t acc_ph = static_cast<uint32_t>(it / nacc) & 1u;
       const int row0 = (tc.m_tile * kCtas + static_cast<int>(cta_rank)) * kTileM + q * 32;
       const int krow = row0 + lane;
       const int n0 = tc.n_tile * p.BN;
+      const int nchunks = tc.bn / 32;
       if (ring && lane == 0) {
         // this warp's first two chunks of the tile: requested before the accumulator is ready
         if (d_tma) bulk_wait_group_read<0>();

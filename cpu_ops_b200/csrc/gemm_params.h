@@ -63,6 +63,7 @@ struct GemmParams {
   int32_t stages;           // smem pipeline depth
   int32_t nacc;             // TMEM accumulator buffers (1 or 2)
   int32_t raster_m;         // m-tiles per raster group (tile walk order)
+  int32_t narrow_last;      // 1: the last tile column is computed at its own (narrower) width
   int32_t a_mn_major, b_mn_major;
   uint32_t idesc;           // instruction descriptor without scale-factor ids
   int32_t mode;             // kModeEpilogue | kModePartial
@@ -82,6 +83,48 @@ struct GemmParams {
   int32_t debug_flags;      // experiments only (CPUOPS_B200_DEBUG)
   unsigned long long* clk_dbg;  // experiments only: {SM cycles, nanoseconds} of CTA 0
 };
+
+// Width at which the last tile column of an n extent is computed when it is computed
+// narrower than the others: the columns it really has, rounded up to the 32 of an
+// epilogue chunk (a legal MMA N for 128- and 256-row tiles).
+__host__ __device__ inline int last_tile_width(int Nk, int BN) {
+  const int rest = Nk - (Nk - 1) / BN * BN;  // 1 .. BN
+  return (rest + 31) & ~31;
+}
+
+// Work order of an unsplit launch whose last tile column is narrower, hence cheaper, than
+// the others.  Work slot v is run by worker v % G (a CTA or a CTA pair) in round v / G.
+// The narrow tiles are dealt to the slots where they even the load out best: first the
+// last round's slots (only the first `e` workers have one), then the round before from
+// worker 0 up (so those same workers end on two narrow tiles instead of a whole extra
+// wide one), and so on downwards; the wide tiles fill the other slots in ascending order.
+// `index` is the narrow tile's number (0 .. narrow - 1) or the wide tile's (0 .. wide - 1).
+struct SlotTile {
+  int narrow, index;
+};
+__host__ __device__ inline SlotTile slot_to_tile(int v, int wide, int narrow, int G) {
+  const int T = wide + narrow;
+  const int R = (T + G - 1) / G;        // rounds
+  const int e = T - (R - 1) * G;        // slots in the last round
+  const int n1 = e < narrow ? e : narrow, n2 = narrow - n1;  // narrow tiles there / below
+  const int i = v / G, c = v - i * G;
+  SlotTile t;
+  int below;  // narrow slots before v
+  if (i == R - 1) {
+    t.narrow = c < n1;
+    t.index = c;
+    below = n2 + (c < n1 ? c : n1);
+  } else {
+    const int q = R - 2 - i;            // rounds between this one and the last
+    const int rem = n2 - q * G;         // narrow tiles left for this round and the earlier ones
+    const int cnt = rem < 0 ? 0 : (rem > G ? G : rem);
+    t.narrow = c < cnt;
+    t.index = n1 + q * G + c;
+    below = (rem > G ? rem - G : 0) + (c < cnt ? c : cnt);
+  }
+  if (!t.narrow) t.index = v - below;
+  return t;
+}
 
 // Shared-memory footprint of one launch of the GEMM kernel.
 __host__ __device__ inline int gemm_stage_bytes(int BN) { return kTileM * 128 + BN * 128; }

@@ -222,6 +222,7 @@ struct EnvSwitches {
   int raster_m = getenv("CPUOPS_B200_RASTER") ? atoi(getenv("CPUOPS_B200_RASTER")) : 0;
   int pair = getenv("CPUOPS_B200_PAIR") ? atoi(getenv("CPUOPS_B200_PAIR")) : -1;  // -1: heuristic
   int ring = getenv("CPUOPS_B200_RING") ? atoi(getenv("CPUOPS_B200_RING")) : 0;    // 0: heuristic
+  bool no_narrow = getenv("CPUOPS_B200_NO_NARROW") != nullptr;
   int epi_warps = getenv("CPUOPS_B200_EPI_WARPS") ? atoi(getenv("CPUOPS_B200_EPI_WARPS")) : 0;
 };
 const EnvSwitches& env_switches() {

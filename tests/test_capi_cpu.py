@@ -148,3 +148,41 @@ def test_last_plan_is_readable_before_any_call(lib):
     plan = _capi.Plan()
     assert lib.cpuops_b200_last_plan(C.byref(plan)) == 0
     assert lib.cpuops_b200_last_plan(None) == _capi.STATUS_INVALID_ARGUMENTS
+
+
+@pytest.mark.parametrize("workers", [1, 3, 74, 148])
+def test_narrow_column_work_order_is_a_permutation_and_balances(lib, workers):
+    """A launch whose last tile column is narrower deals those cheaper tiles to the work
+    slots (slot v runs on worker v % workers in round v // workers) so that no worker ends
+    a whole wide tile late.  The map must hit every tile exactly once, keep the wide tiles
+    in ascending order, and never load a worker more than the plain order would."""
+    f = lib.cpuops_b200_debug_slot_to_tile
+    f.argtypes = [C.c_int32] * 4 + [C.POINTER(C.c_int32)] * 2
+    f.restype = C.c_int
+
+    def loads(wide, narrow, order):
+        out = [0.0] * workers
+        for v, is_narrow in enumerate(order):
+            out[v % workers] += 0.67 if is_narrow else 1.0
+        return max(out)
+
+    for narrow in (0, 1, 2, 16, 33):
+        for wide in (0, 1, 73, 74, 147, 288, 301):
+            if wide + narrow == 0:
+                continue
+            wide_seen, narrow_seen, order = [], set(), []
+            for v in range(wide + narrow):
+                a, b = C.c_int32(), C.c_int32()
+                assert f(v, wide, narrow, workers, C.byref(a), C.byref(b)) == 0
+                order.append(bool(a.value))
+                if a.value:
+                    assert 0 <= b.value < narrow and b.value not in narrow_seen
+                    narrow_seen.add(b.value)
+                else:
+                    wide_seen.append(b.value)
+            assert wide_seen == list(range(wide))
+            assert len(narrow_seen) == narrow
+            plain = [False] * wide + [True] * narrow
+            assert loads(wide, narrow, order) <= loads(wide, narrow, plain) + 1e-9
+    a, b = C.c_int32(), C.c_int32()
+    assert f(5, 2, 3, workers, C.byref(a), C.byref(b)) == 1      # slot out of range
