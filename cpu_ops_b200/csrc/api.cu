@@ -975,7 +975,15 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     }
     p.ring_bufs = (p.c_ring || p.d_tma) ? 2 : 0;
     if (p.ring_bufs && env_switches().ring == 3) p.ring_bufs = 3;
-    const int epi_warps = env_switches().epi_warps == 8 ? 8 : 4;
+    // Eight epilogue warps (two per tensor-memory lane quarter) when no CTA gets a second
+    // tile to hide its epilogue behind and the tile is wide enough to share out; otherwise
+    // four, which leave more shared memory to the k pipeline.
+    int epi_warps = 4;
+    {
+      const int64_t items = static_cast<int64_t>(p.m_tiles) * p.n_tiles * p.slices;
+      if (!ch.pair && items <= st.sm_count && ch.BN >= 128) epi_warps = 8;
+      if (env_switches().epi_warps == 8 || env_switches().epi_warps == 4) epi_warps = env_switches().epi_warps;
+    }
     p.error = st.error_dev;
     p.debug_flags = env_switches().debug_flags;
     if (env_switches().clk) {
