@@ -101,3 +101,22 @@ def test_mx_pair_tile_widths_and_split_k(gpu, oracle, tile_n):
         ref = run_mx_oracle(oracle, P, 1.0, 0.5, slices=1)
         G, R = gather(D, P.m, P.n, P.ldc, True), gather(ref, P.m, P.n, P.ldc, True)
         assert np.linalg.norm(G.astype(np.float64) - R) <= 1e-5 * np.linalg.norm(R)
+
+
+@pytest.mark.parametrize("pair", [False, True])
+def test_narrow_last_column_over_several_rounds(gpu, oracle, pair):
+    """More tiles than workers and a ragged last tile column: that column is computed at
+    its own width and its tiles are dealt to the late work slots.  Every tile must still be
+    computed exactly once: int8 bit-exact, MX within the tolerance."""
+    m, n, k = 4096, 1300, 256            # 256-wide tiles: five full columns + one of 20
+    P = W.int8_problem(m, n, k, 1, 0, 1, pad=4, seed=91)
+    st, D = run_int8_gpu(P, alpha=2, beta=1, pair=pair, tile_n=256)
+    assert st == c.Status.kSuccess, _capi.last_error()
+    _assert_pair(1 if pair else 0)
+    want = run_int8_oracle(oracle, P, alpha=2, beta=1)
+    assert np.array_equal(gather(D, m, n, P.ldc, 1), gather(want, m, n, P.ldc, 1))
+    Q = W.mx_problem(FMT_E4M3, m, 1100, 512, True, pad=0, seed=92)
+    st, D = run_mx_gpu(Q, 1.0, 0.5, pair=pair, tile_n=192)           # five full columns + 140 -> 160 wide
+    assert st == c.Status.kSuccess, _capi.last_error()
+    _assert_pair(1 if pair else 0)
+    check_mx(oracle, Q, D, 1.0, 0.5)
