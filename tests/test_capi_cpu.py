@@ -186,3 +186,24 @@ def test_narrow_column_work_order_is_a_permutation_and_balances(lib, workers):
             assert loads(wide, narrow, order) <= loads(wide, narrow, plain) + 1e-9
     a, b = C.c_int32(), C.c_int32()
     assert f(5, 2, 3, workers, C.byref(a), C.byref(b)) == 1      # slot out of range
+
+
+def test_tile_width_choice_for_the_configured_workloads(lib):
+    """The launcher's cost model (148 SMs): 256-wide tiles for int8, 224-wide for MX (two
+    accumulators plus the scale slots must fit in tensor memory), also for 4096^3 where a
+    64-wide last column evens the rounds out; an n-contiguous B only allows 128 or 256."""
+    f = lib.cpuops_b200_debug_pick_tile_width
+    f.argtypes = [C.c_int32] * 7
+    f.restype = C.c_int
+    sms = 148
+    #            Mk     Nk     k-blocks  mx beta  n-contiguous B
+    assert f(4096, 4096, 32, 1, sms, 1, 0) == 224          # mxfp8 4096^3, beta = 0.5
+    assert f(8192, 8192, 64, 1, sms, 0, 0) == 224          # mxfp8 8192^3
+    assert f(16384, 16384, 64, 1, sms, 0, 0) == 224        # mxfp4 16384^3
+    assert f(8192, 8192, 64, 0, sms, 0, 1) == 256          # int8 8192^3, row-major B
+    assert f(8192, 8192, 128, 0, sms, 0, 1) == 256         # int8 8192 x 8192 x 16384
+    assert f(2048, 2048, 16, 0, sms, 1, 1) == 256          # int8 2048^3
+    for nk in (129, 500, 1000, 3000, 5000):
+        for mk in (128, 1000, 5000):
+            assert f(mk, nk, 16, 0, sms, 0, 1) in (128, 256)
+            assert f(mk, nk, 16, 1, sms, 1, 0) in (128, 160, 192, 224, 256)
