@@ -302,7 +302,7 @@ CPUOPS_B200_API int cpuops_b200_debug_clock(unsigned long long* out) {
   if (!g_clk_buf || !out) return 1;
   cudaDeviceSynchronize();
   // [8],[9]: first CTA start / last CTA end (ns)
-  cudaMemcpy(out, g_clk_buf, 12 * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+  cudaMemcpy(out, g_clk_buf, 16 * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
   return 0;
 }
 
@@ -990,6 +990,7 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
       if (!g_clk_buf) cudaMalloc(&g_clk_buf, 128);
       cudaMemsetAsync(g_clk_buf + 8, 0xFF, 8, stream);
       cudaMemsetAsync(g_clk_buf + 9, 0, 8, stream);
+      cudaMemsetAsync(g_clk_buf + 12, 0xFF, 8, stream);  // [12]: first CTA entry (ns)
       p.clk_dbg = g_clk_buf;
     }
     const int sf_stage_bytes = p.sfa_stage_bytes + p.sfb_stage_bytes;

@@ -193,6 +193,7 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
   const uint32_t smem_base = raw_addr + pad;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (p.clk_dbg != nullptr && threadIdx.x == 0) atomicMin(p.clk_dbg + 12, global_timer_ns());
   const int stages = p.stages;
   const int b_rows = p.BN / kCtas;  // rows of the B tile staged by this CTA
   const int stage_bytes = gemm_stage_bytes(b_rows);
