@@ -72,6 +72,15 @@ int pick_bn_for_small(int nk) {
 // (about 64 bytes per clock per SM) rather than by the MMA itself (BN / 2 clocks per
 // 32-byte k step), so a k-block costs 2 * (128 + BN) clocks; the epilogue overlaps
 // the next tile's k loop only when there are two accumulator buffers.
+// Load of the busiest worker when `wide` tiles of cost cw and `narrow` tiles of cost cn
+// are dealt to the workers the way the kernel does it (slot_to_tile).
+double busiest_worker(int wide, int narrow, int workers, double cw, double cn) {
+  std::vector<double> load(static_cast<size_t>(workers), 0.0);
+  for (int v = 0; v < wide + narrow; ++v)
+    load[static_cast<size_t>(v % workers)] += slot_to_tile(v, wide, narrow, workers).narrow ? cn : cw;
+  return *std::max_element(load.begin(), load.end());
+}
+
 // Whether a launch runs as pairs of CTAs on 256-row tiles (see gemm_body).
 bool pair_pays(int Mk, int Nk, int k_blocks, int BN, int slices, int sms, bool bk_role_mn) {
   const int64_t tiles = static_cast<int64_t>((Mk + 127) / 128) * ((Nk + BN - 1) / BN) * slices;
@@ -85,27 +94,39 @@ bool pair_pays(int Mk, int Nk, int k_blocks, int BN, int slices, int sms, bool b
 // behind the next tile's k loop when there are two accumulators.  The tiles are dealt to
 // the workers (CTAs or pairs) round-robin, and a ragged last tile column is cheaper when it
 // can be computed at its own width (slot_to_tile), so the cost is the busiest worker's.
-double config_cost(int Mk, int Nk, int k_blocks, int BN, int nacc, int sms, bool beta, bool bk_role_mn) {
+double config_cost(int Mk, int Nk, int k_blocks, int BN, int nacc, int sms, bool beta, bool bk_role_mn,
+                   bool is_mx) {
   const bool pair = pair_pays(Mk, Nk, k_blocks, BN, 1, sms, bk_role_mn);
   const int tile_m = pair ? 256 : 128;
   const int m_tiles = (Mk + tile_m - 1) / tile_m, n_tiles = (Nk + BN - 1) / BN;
   const int workers = std::max(1, pair ? sms / 2 : sms);
-  auto tile_cost = [&](int width) {
+  auto tile_cost = [&](int width, double* epilogue) {
     const double b_rows = pair ? width / 2.0 : width;
-    const double kblock = std::max(2.0 * width, 2.0 * (128.0 + b_rows));
-    const double epi = 128.0 * width * (beta ? 8.0 : 4.0) / 20.0;  // ~20 B/clk/SM of HBM
-    return k_blocks * kblock + (nacc == 1 ? epi : 0.15 * epi);
+    // (MX k-blocks have not been seen below ~600 cycles whatever the tile: four loads,
+    // scale copies, barrier round trips)
+    const double kblock = std::max({2.0 * width, 2.0 * (128.0 + b_rows), is_mx ? 600.0 : 0.0});
+    // the epilogue: four warps drain a 32-column chunk in about 1500 cycles each (latency
+    // bound), or what HBM takes at ~20 B/clk/SM; with two accumulators it runs beside the next
+    // tile's k loop, which then lasts at least as long
+    // (half that with eight epilogue warps, which short k loops and single-wave launches get)
+    const bool eight = width >= 128 && (2 * k_blocks <= 3 * (width / 32) ||
+                                        (!pair && static_cast<int64_t>(m_tiles) * n_tiles <= sms));
+    const double epi = std::max(width / 32 * (eight ? 750.0 : 1500.0), 128.0 * width * (beta ? 8.0 : 4.0) / 25.0);
+    if (epilogue) *epilogue = epi;
+    return nacc == 1 ? 1.03 * (k_blocks * kblock + epi) : std::max(k_blocks * kblock, epi) + 0.1 * epi;
   };
   const int last = last_tile_width(Nk, BN);
   const bool narrow_last = !bk_role_mn && n_tiles >= 2 && last < BN;
   const int narrow = narrow_last ? m_tiles : 0, wide = m_tiles * n_tiles - narrow;
-  const double cw = tile_cost(BN), cn = narrow_last ? tile_cost(last) : cw;
+  double cw_epilogue = 0.0;
+  const double cw = tile_cost(BN, &cw_epilogue), cn = narrow_last ? tile_cost(last, nullptr) : cw;
+  // nothing hides the epilogue of a worker's last tile
+  const double tail = nacc == 1 ? 0.0 : 0.5 * cw_epilogue;
   const int64_t total = static_cast<int64_t>(wide) + narrow;
-  if (total > 64ll * workers) return (wide * cw + narrow * cn) / workers + cw;  // rounding is noise
-  std::vector<double> load(static_cast<size_t>(workers), 0.0);
-  for (int v = 0; v < total; ++v)
-    load[static_cast<size_t>(v % workers)] += slot_to_tile(v, wide, narrow, workers).narrow ? cn : cw;
-  return *std::max_element(load.begin(), load.end());
+  // when in doubt the wider tile: it moves fewer operand bytes per output
+  const double bias = 1.0 + 0.1 * (256 - BN) / 128.0;
+  if (total > 64ll * workers) return bias * ((wide * cw + narrow * cn) / workers + cw + tail);  // rounding is noise
+  return bias * (busiest_worker(wide, narrow, workers, cw, cn) + tail);
 }
 
 // Tile width for a kernel-view n extent above 128: the cheapest of the candidates.
@@ -115,7 +136,7 @@ int pick_tile_width(int Mk, int Nk, int k_blocks, bool is_mx, int sms, bool beta
   for (int bn : {256, 224, 192, 160, 128}) {
     if (bk_role_mn && bn % 128 != 0) continue;
     const int nacc = (is_mx && bn > 224) ? 1 : 2;  // MX: the scale slots need tensor-memory columns too
-    const double c = config_cost(Mk, Nk, k_blocks, bn, nacc, sms, beta, bk_role_mn);
+    const double c = config_cost(Mk, Nk, k_blocks, bn, nacc, sms, beta, bk_role_mn, is_mx);
     if (c < best) {
       best = c;
       width = bn;
@@ -590,10 +611,19 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
       const double block_us = std::max(gemm_stage_bytes(ch.BN) / per_sm,
                                        4.0 * std::max(ch.BN / 2.0, (128.0 + ch.BN) / 4.0) / 1500.0);
       double best = 1e300;
+      // unsplit, a ragged last tile column is computed narrower and dealt out evenly:
+      // rounds in units of a wide tile (feed-bound cost ~ 128 + width rows per k-block)
+      double rounds1 = static_cast<double>((tiles + st.sm_count - 1) / st.sm_count);
+      {
+        const int n_tiles = (Nk + ch.BN - 1) / ch.BN, m_tiles = (Mk + 127) / 128, last = last_tile_width(Nk, ch.BN);
+        if (!bk_role_mn && n_tiles >= 2 && last < ch.BN && !env_switches().no_narrow)
+          rounds1 = busiest_worker(m_tiles * (n_tiles - 1), m_tiles, st.sm_count, 1.0,
+                                   (128.0 + last) / (128.0 + ch.BN));
+      }
       for (int s = 1; s <= std::min(32, k_blocks / 2); ++s) {
         const int64_t waves = (tiles * s + st.sm_count - 1) / st.sm_count;
         const int per_slice = (k_blocks + s - 1) / s;
-        double t_us = static_cast<double>(waves) * per_slice * block_us;
+        double t_us = (s == 1 ? rounds1 : static_cast<double>(waves)) * per_slice * block_us;
         if (s > 1) t_us += 2.0 * s * Mk * static_cast<double>(Nk) * 4.0 / hbm_bytes_per_us + 3.0;
         if (t_us < best * 0.97) {
           best = t_us;
@@ -982,6 +1012,10 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     {
       const int64_t items = static_cast<int64_t>(p.m_tiles) * p.n_tiles * p.slices;
       if (!ch.pair && items <= st.sm_count && ch.BN >= 128) epi_warps = 8;
+      // ... or when k is so short that a tile's k loop (about 600 cycles per k-block) ends
+      // well before four warps have drained the previous tile (about 1500 cycles per
+      // 32-column chunk each): measured +10-15 % at K = 1024, nothing at K = 2048
+      if (2 * (k_blocks / ch.slices) <= 3 * (ch.BN / 32) && ch.BN >= 128) epi_warps = 8;
       if (env_switches().epi_warps == 8 || env_switches().epi_warps == 4) epi_warps = env_switches().epi_warps;
     }
     p.error = st.error_dev;
