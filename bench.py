@@ -633,6 +633,7 @@ def main():
 KERNEL_DRAM_TRAFFIC = {
     "mxfp8_e4m3_4096": 123.07e6 + 38.85e6,
     "int8_8192": 367.55e6 + 235.98e6,
+    "int8_2048": 25.24e6,
     "mxfp4_decode_m8": 31.32e6,
 }
 
