@@ -56,7 +56,8 @@ class Plan(C.Structure):
     """cpuops_b200_plan: what the last GEMM call launched (diagnostics)."""
     _fields_ = [("swapped", C.c_int32), ("tile_n", C.c_int32), ("pair", C.c_int32),
                 ("slices", C.c_int32), ("stages", C.c_int32), ("grid", C.c_int32),
-                ("c_ring", C.c_int32), ("prepared_b", C.c_int32)]
+                ("c_ring", C.c_int32), ("prepared_b", C.c_int32),
+                ("epilogue_warps", C.c_int32), ("narrow_last", C.c_int32)]
 
 
 class Scalar(C.Union):

@@ -1111,6 +1111,8 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     g_last_plan.grid = static_cast<int32_t>(grid);
     g_last_plan.c_ring = p.c_ring;
     g_last_plan.prepared_b = used_prepared ? 1 : 0;
+    g_last_plan.epilogue_warps = epi_warps;
+    g_last_plan.narrow_last = p.narrow_last;
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
     if (kind == kKindI8) {

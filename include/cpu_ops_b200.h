@@ -237,6 +237,8 @@ typedef struct cpuops_b200_plan {
   int32_t grid;      /* CTAs launched                                             */
   int32_t c_ring;    /* 1: C prefetched by TMA into shared memory                  */
   int32_t prepared_b; /* 1: B's scale atoms came from cpuops_b200_prepare_b        */
+  int32_t epilogue_warps; /* 4, or 8 (single-wave launches and short k loops)      */
+  int32_t narrow_last;    /* 1: a ragged last tile column ran at its own width     */
 } cpuops_b200_plan;
 CPUOPS_B200_API int cpuops_b200_last_plan(cpuops_b200_plan* out);
 

@@ -103,6 +103,16 @@ def test_mx_pair_tile_widths_and_split_k(gpu, oracle, tile_n):
         assert np.linalg.norm(G.astype(np.float64) - R) <= 1e-5 * np.linalg.norm(R)
 
 
+def _int8_on_device(P, **kw):
+    """The whole problem resident on the device: one kernel launch, no host row panels."""
+    import torch
+    dev = torch.device("cuda", 0)
+    bufs = {name: torch.from_numpy(getattr(P, name)).to(dev) for name in ("A", "B", "C")}
+    bufs["D"] = torch.full((P.C.size,), -(1 << 31), device=dev, dtype=torch.int32)
+    st, _ = run_int8_gpu(P, bufs=bufs, **kw)
+    return st, bufs["D"].cpu().numpy()
+
+
 @pytest.mark.parametrize("pair", [False, True])
 def test_narrow_last_column_over_several_rounds(gpu, oracle, pair):
     """More tiles than workers and a ragged last tile column: that column is computed at
@@ -110,13 +120,29 @@ def test_narrow_last_column_over_several_rounds(gpu, oracle, pair):
     computed exactly once: int8 bit-exact, MX within the tolerance."""
     m, n, k = 4096, 1300, 256            # 256-wide tiles: five full columns + one of 20
     P = W.int8_problem(m, n, k, 1, 0, 1, pad=4, seed=91)
-    st, D = run_int8_gpu(P, alpha=2, beta=1, pair=pair, tile_n=256)
+    st, D = _int8_on_device(P, alpha=2, beta=1, pair=pair, tile_n=256)
     assert st == c.Status.kSuccess, _capi.last_error()
     _assert_pair(1 if pair else 0)
+    plan = _capi.last_plan()
+    assert plan.narrow_last == 1 and plan.grid == 148      # 192 (96) tiles on 148 CTAs (74 pairs)
     want = run_int8_oracle(oracle, P, alpha=2, beta=1)
     assert np.array_equal(gather(D, m, n, P.ldc, 1), gather(want, m, n, P.ldc, 1))
     Q = W.mx_problem(FMT_E4M3, m, 1100, 512, True, pad=0, seed=92)
     st, D = run_mx_gpu(Q, 1.0, 0.5, pair=pair, tile_n=192)           # five full columns + 140 -> 160 wide
     assert st == c.Status.kSuccess, _capi.last_error()
     _assert_pair(1 if pair else 0)
+    assert _capi.last_plan().narrow_last == 1
     check_mx(oracle, Q, D, 1.0, 0.5)
+
+
+def test_epilogue_warp_count_follows_the_launch_shape(gpu, oracle):
+    """Eight epilogue warps when no CTA gets a second tile or the k loop is short, four
+    otherwise; both forms must give the oracle's bits."""
+    for (m, n, k), want_warps in (((1024, 1024, 512), 8),      # 32 tiles on 148 SMs: a single wave
+                                  ((4096, 2048, 512), 8),      # several waves, 4 k-blocks per tile
+                                  ((4096, 2048, 4096), 4)):    # several waves, 32 k-blocks per tile
+        P = W.int8_problem(m, n, k, 1, 0, 1, seed=m + k)
+        st, D = _int8_on_device(P, alpha=1, beta=1, tile_n=256)
+        assert st == c.Status.kSuccess, _capi.last_error()
+        assert _capi.last_plan().epilogue_warps == want_warps, (m, n, k)
+        assert np.array_equal(D, run_int8_oracle(oracle, P, alpha=1, beta=1))
