@@ -203,6 +203,14 @@ def test_tile_width_choice_for_the_configured_workloads(lib):
     assert f(8192, 8192, 64, 0, sms, 0, 1) == 256          # int8 8192^3, row-major B
     assert f(8192, 8192, 128, 0, sms, 0, 1) == 256         # int8 8192 x 8192 x 16384
     assert f(2048, 2048, 16, 0, sms, 1, 1) == 256          # int8 2048^3
+    # mid-size shapes whose choice was checked against forced widths on a B200
+    assert f(2048, 2048, 16, 1, sms, 0, 0) == 256          # MX 2048^3: one wave of 128 tiles
+    assert f(1024, 4096, 32, 1, sms, 0, 0) == 256          # 224 would be 152 tiles on 148 SMs
+    assert f(4096, 1024, 32, 1, sms, 1, 0) == 256
+    assert f(3000, 5000, 16, 1, sms, 0, 0) == 224
+    assert f(1024, 8192, 16, 1, sms, 0, 0) == 224
+    assert f(2560, 2560, 64, 1, sms, 0, 0) in (192, 224)   # not 128-wide pairs: 15 % slower
+    assert f(1024, 4096, 32, 0, sms, 0, 1) == 256
     for nk in (129, 500, 1000, 3000, 5000):
         for mk in (128, 1000, 5000):
             assert f(mk, nk, 16, 0, sms, 0, 1) in (128, 256)
