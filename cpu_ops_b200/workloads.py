@@ -106,15 +106,17 @@ class MxProblem:
 
 
 def mx_problem(fmt, m, n, k, c_rm=True, pad=0, scale_lo=124, scale_hi=130, seed=0, fmt_b=None,
-               c_sigma=1.0, finite_only=True) -> MxProblem:
-    """MX operands in the TN layout (A: m rows of k, B: n rows of k)."""
+               c_sigma=1.0, finite_only=True, lds=None) -> MxProblem:
+    """MX operands in the TN layout (A: m rows of k, B: n rows of k).  `lds` overrides the
+    leading dimension of both scale arrays (default: ceil(k/32), one more when padded)."""
     fmt_b = fmt if fmt_b is None else fmt_b
     even = 1 if (fmt == _capi.FMT_E2M1 or fmt_b == _capi.FMT_E2M1) else 0
     ld = k + pad
     if even and (ld & 1):
         ld += 1
     kg = (k + 31) // 32
-    lds = kg + (1 if pad else 0)
+    lds = (kg + (1 if pad else 0)) if lds is None else int(lds)
+    assert lds >= kg
     ldc = (n if c_rm else m) + pad
     r = rng_for(seed, 2)
     A = mx_elements(fmt, m, k, ld, r, finite_only)
