@@ -30,6 +30,7 @@ OP_RELU, OP_CLAMP, OP_BIAS_ADD, OP_SCALE_PER_ROW, OP_SCALE_PER_COL, OP_GELU, OP_
 MEM_AUTO, MEM_HOST, MEM_DEVICE = 0, 1, 2
 FLAG_ASYNC = 1
 FLAG_PAIR_ON, FLAG_PAIR_OFF = 2, 4
+FLAG_B_IMMUTABLE = 8
 NOALLOC_SCRATCH_BYTES = 8 << 20
 
 # Every symbol include/cpu_ops_b200.h declares.
@@ -40,6 +41,8 @@ EXPORTED_SYMBOLS = (
     "cpuops_b200_scale_layout_bytes",
     "cpuops_b200_shard_rows",
     "cpuops_b200_stream_status",
+    "cpuops_b200_set_wait_budget_us",
+    "cpuops_b200_selftest_wait_timeout",
     "cpuops_b200_profile",
     "cpuops_b200_profile_collect",
     "cpuops_b200_launch_count",
@@ -57,7 +60,7 @@ class Plan(C.Structure):
     _fields_ = [("swapped", C.c_int32), ("tile_n", C.c_int32), ("pair", C.c_int32),
                 ("slices", C.c_int32), ("stages", C.c_int32), ("grid", C.c_int32),
                 ("c_ring", C.c_int32), ("prepared_b", C.c_int32),
-                ("epilogue_warps", C.c_int32), ("narrow_last", C.c_int32)]
+                ("epilogue_warps", C.c_int32), ("narrow_last", C.c_int32), ("decode", C.c_int32)]
 
 
 class Scalar(C.Union):
@@ -111,6 +114,10 @@ def load() -> C.CDLL:
                                            C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
     lib.cpuops_b200_stream_status.restype = C.c_int
     lib.cpuops_b200_stream_status.argtypes = [C.c_void_p]
+    lib.cpuops_b200_set_wait_budget_us.restype = C.c_int
+    lib.cpuops_b200_set_wait_budget_us.argtypes = [C.c_uint32]
+    lib.cpuops_b200_selftest_wait_timeout.restype = C.c_int
+    lib.cpuops_b200_selftest_wait_timeout.argtypes = [C.c_uint32, C.c_void_p]
     lib.cpuops_b200_profile.restype = C.c_int
     lib.cpuops_b200_profile.argtypes = [C.c_int]
     lib.cpuops_b200_profile_collect.restype = C.c_int

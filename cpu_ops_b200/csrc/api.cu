@@ -145,6 +145,77 @@ int pick_tile_width(int Mk, int Nk, int k_blocks, bool is_mx, int sms, bool beta
   return width;
 }
 
+// ---- small-m MX problems: the decode kernel (decode_kernel.cuh) ------------------------
+
+struct DecodePlan {
+  bool use = false;
+  int BN = 32, tiles = 0, grid = 0, stages = 0, tile_aligned = 0, max_pieces = 1, tmem_cols = 128, w_early = 0;
+  size_t partial_bytes = 0;
+  int smem = 0;
+};
+
+// Grid, ranges and buffers of a decode launch: Mk weight rows (128-row tiles), Nk <= 64
+// activation rows, k_blocks 128-byte k-blocks.  Every CTA takes an equal share of the
+// (tile, k-block) units; `never_split` (split_k_slices == 1) keeps whole tiles together.
+DecodePlan plan_decode(const DeviceState& st, int kind, int Mk, int Nk, int k_blocks, bool never_split,
+                       bool w_immutable) {
+  DecodePlan dp;
+  dp.use = true;
+  dp.w_early = w_immutable ? 1 : 0;
+  dp.BN = Nk <= 32 ? 32 : 64;
+  dp.tiles = (Mk + kTileM - 1) / kTileM;
+  const int ka = kind == kKindMxf4 ? 2 : 1;
+  const int per_stage = decode_stage_bytes(Nk) + 2 * ka * 512;
+  // One CTA per SM with the deepest ring the shared memory allows (the stream needs the
+  // bytes in flight).  With immutable weights two smaller CTAs fit an SM instead, so that the
+  // next call's CTAs are resident, their first ring of W already loading, while this call's
+  // are still streaming.
+  int ctas_per_sm = w_immutable ? 2 : 1;
+  if (env_switches().decode_ctas_per_sm > 0) ctas_per_sm = env_switches().decode_ctas_per_sm;
+  const int64_t units = static_cast<int64_t>(dp.tiles) * k_blocks;
+  const int cap = st.sm_count * ctas_per_sm;
+  int grid;
+  if (never_split || 4 * dp.tiles >= cap) {
+    // whole tiles per CTA: no partial sums.  (Measured on 112 tiles: cutting k to feed all
+    // 148 SMs does not shorten the stream, and the reduction through L2 costs 4 us.)
+    grid = std::min(dp.tiles, cap);
+    dp.tile_aligned = 1;
+  } else {
+    grid = static_cast<int>(std::min<int64_t>(cap, std::max<int64_t>(1, units / 4)));  // >= 4 units per CTA
+    if (dp.tiles >= grid && dp.tiles % grid == 0) dp.tile_aligned = 1;
+  }
+  if (env_switches().decode_grid > 0 && !never_split) {
+    grid = static_cast<int>(std::min<int64_t>(env_switches().decode_grid, units));
+    dp.tile_aligned = (dp.tiles % grid == 0) ? 1 : 0;
+  }
+  dp.grid = grid;
+  const int budget = st.smem_optin / ctas_per_sm - (ctas_per_sm > 1 ? 1024 : 0);
+  int stages = (budget - 1024 - decode_staging_bytes(dp.BN) - kDecodeBarrierBytes) / per_stage;
+  stages = std::min({stages, kDecodeMaxStages, static_cast<int>(std::max<int64_t>(2, (units + grid - 1) / grid))});
+  if (env_switches().decode_stages > 0) stages = std::min(stages, env_switches().decode_stages);
+  dp.stages = std::max(2, stages);
+  dp.smem = decode_smem_bytes(Nk, dp.BN, dp.stages, 2 * ka);
+  // one CTA per SM must not be joined by a second one that would queue behind its TMEM
+  if (ctas_per_sm == 1) dp.smem = std::max(dp.smem, 120 * 1024);
+  const int sf_cols = 4 * 2 * ka;
+  int cols = 2 * dp.BN + kDecodeSfSlots * sf_cols;
+  dp.tmem_cols = 32;
+  while (dp.tmem_cols < cols) dp.tmem_cols *= 2;
+  if (!dp.tile_aligned) {
+    DecodeParams q;
+    memset(&q, 0, sizeof(q));
+    q.tiles = dp.tiles;
+    q.k_blocks = k_blocks;
+    for (int t = 0; t < dp.tiles; ++t) {
+      const int first = decode_cta_of_unit(q, static_cast<int64_t>(t) * k_blocks, grid);
+      const int last = decode_cta_of_unit(q, static_cast<int64_t>(t + 1) * k_blocks - 1, grid);
+      dp.max_pieces = std::max(dp.max_pieces, last - first + 1);
+    }
+    dp.partial_bytes = static_cast<size_t>(dp.tiles) * dp.max_pieces * dp.BN * kTileM * 4;
+  }
+  return dp;
+}
+
 }  // namespace
 
 // =================================================================================
@@ -167,13 +238,14 @@ CPUOPS_B200_API int cpuops_b200_prepare_b(const cpuops_b200_gemm_desc* d, void**
     set_error("prepare_b: invalid B scale description");
     return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
   }
-  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceRestore restore;
   DeviceState* st = nullptr;
   if (int rc = init_device(d->device, &st)) return rc;
   if (!is_device_pointer(d->b_scales, d->memory_space)) {
     set_error("prepare_b: the B scales must live in device memory");
     return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
   }
+  std::lock_guard<std::mutex> lk(g_registry_mu);
   PreparedB* pb = find_prepared(st->device, d->b_scales, d->n, d->k, d->ld_scales_b);
   if (!pb) {
     pb = new PreparedB{st->device, d->b_scales, d->n, d->k, d->ld_scales_b, {}};
@@ -184,22 +256,31 @@ CPUOPS_B200_API int cpuops_b200_prepare_b(const cpuops_b200_gemm_desc* d, void**
 }
 
 CPUOPS_B200_API int cpuops_b200_release_b(void* handle) {
-  std::lock_guard<std::mutex> lk(g_mu);
-  for (size_t i = 0; i < g_prepared.size(); ++i) {
-    if (g_prepared[i] != handle) continue;
-    PreparedB* pb = g_prepared[i];
-    cudaSetDevice(pb->device);
-    cudaDeviceSynchronize();  // no kernel may still be reading the kept copies
-    for (PreparedLayout& pl : pb->layouts) cudaFree(pl.atoms);
-    delete pb;
-    g_prepared.erase(g_prepared.begin() + static_cast<long>(i));
-    return CPUOPS_B200_STATUS_SUCCESS;
+  PreparedB* pb = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_registry_mu);
+    for (size_t i = 0; i < g_prepared.size(); ++i) {
+      if (g_prepared[i] != handle) continue;
+      pb = g_prepared[i];
+      g_prepared.erase(g_prepared.begin() + static_cast<long>(i));
+      break;
+    }
   }
-  set_error("release_b: unknown handle");
-  return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+  if (!pb) {
+    set_error("release_b: unknown handle");
+    return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+  }
+  DeviceRestore restore;  // the caller's current device is put back on return
+  std::lock_guard<std::mutex> dev_lk(g_dev[pb->device].mu);
+  cudaSetDevice(pb->device);
+  cudaDeviceSynchronize();  // no kernel may still be reading the kept copies
+  for (PreparedLayout& pl : pb->layouts) cudaFree(pl.atoms);
+  delete pb;
+  return CPUOPS_B200_STATUS_SUCCESS;
 }
 
-// Undeclared (tests only): the work order of a launch with a narrow last tile column.
+#ifdef CPUOPS_B200_INSTRUMENT
+// Instrumented build only (tests): the work order of a launch with a narrow last tile column.
 CPUOPS_B200_API int cpuops_b200_debug_slot_to_tile(int32_t v, int32_t wide, int32_t narrow, int32_t workers,
                                                    int32_t* is_narrow, int32_t* index) {
   if (!is_narrow || !index || workers <= 0 || wide < 0 || narrow < 0 || v < 0 || v >= wide + narrow) return 1;
@@ -215,17 +296,35 @@ CPUOPS_B200_API int cpuops_b200_debug_pick_tile_width(int32_t Mk, int32_t Nk, in
   return pick_tile_width(Mk, Nk, k_blocks, is_mx != 0, sms, beta != 0, n_contiguous_b != 0);
 }
 
+// Instrumented build only: {SM cycles, ns} of CTA 0 of the last GEMM kernel when
+// CPUOPS_B200_CLK is set; [8], [9]: first CTA start / last CTA end (ns).
+CPUOPS_B200_API int cpuops_b200_debug_clock(unsigned long long* out) {
+  if (!g_clk_buf || !out) return 1;
+  cudaDeviceSynchronize();
+  cudaMemcpy(out, g_clk_buf, 16 * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+  return 0;
+}
+
+// Instrumented build only: the decode kernel's role stamps of the last sixteen launches
+// (16 words each; see DECODE_STAMP), then clears them.
+CPUOPS_B200_API int cpuops_b200_debug_decode_clock(unsigned long long* out, int32_t* launches) {
+  if (!g_decode_clk || !out) return 1;
+  cudaDeviceSynchronize();
+  cudaMemcpy(out, g_decode_clk, 16 * 16 * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+  cudaMemset(g_decode_clk, 0, 16 * 16 * sizeof(unsigned long long));
+  if (launches) *launches = static_cast<int32_t>(g_decode_clk_launch);
+  g_decode_clk_launch = 0;
+  return 0;
+}
+#endif  // CPUOPS_B200_INSTRUMENT
+
 CPUOPS_B200_API int cpuops_b200_last_plan(cpuops_b200_plan* out) {
   if (!out) return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
-  std::lock_guard<std::mutex> lk(g_mu);
   *out = g_last_plan;
   return 0;
 }
 
-CPUOPS_B200_API int cpuops_b200_device_count(void) {
-  std::lock_guard<std::mutex> lk(g_mu);
-  return probe_devices();
-}
+CPUOPS_B200_API int cpuops_b200_device_count(void) { return probe_devices(); }
 
 CPUOPS_B200_API int cpuops_b200_shard_rows(int32_t m, int32_t world, int32_t rank,
                                            int32_t* row_begin, int32_t* row_count) {
@@ -285,7 +384,6 @@ static int launch_relayout(const void* src0, void* dst0, const ScaleLayout& L0, 
 CPUOPS_B200_API int cpuops_b200_relayout_scales(const void* scales, int32_t rows, int32_t k,
                                                 int32_t ld_scales, int32_t tile_rows,
                                                 int32_t blocks_per_stage, void* out, void* stream) {
-  std::lock_guard<std::mutex> lk(g_mu);
   if (!scales || !out || rows <= 0 || k <= 0 || ld_scales < (k + 31) / 32 || tile_rows <= 0 ||
       tile_rows % 32 != 0 || (blocks_per_stage != 4 && blocks_per_stage != 8)) {
     set_error("relayout_scales: invalid arguments");
@@ -293,6 +391,7 @@ CPUOPS_B200_API int cpuops_b200_relayout_scales(const void* scales, int32_t rows
   }
   DeviceState* st = nullptr;
   if (int rc = init_device(-1, &st)) return rc;
+  std::lock_guard<std::mutex> lk(st->mu);
   cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : st->stream;
   const ScaleLayout L = make_scale_layout(rows, k, ld_scales, tile_rows, blocks_per_stage);
   if (int rc = launch_relayout(scales, out, L, nullptr, nullptr, L, s)) return rc;
@@ -301,10 +400,41 @@ CPUOPS_B200_API int cpuops_b200_relayout_scales(const void* scales, int32_t rows
 }
 
 CPUOPS_B200_API int cpuops_b200_stream_status(void* stream) {
-  std::lock_guard<std::mutex> lk(g_mu);
   DeviceState* st = nullptr;
   if (int rc = init_device(-1, &st)) return rc;
+  std::lock_guard<std::mutex> lk(st->mu);
   cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : st->stream;
+  CUDA_TRY(cudaMemcpyAsync(st->error_host, st->error_dev, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+  CUDA_TRY(cudaStreamSynchronize(s));
+  if (*st->error_host != 0) {
+    set_error("device-side bounded wait timed out (code %d)", *st->error_host);
+    *st->error_host = 0;
+    CUDA_TRY(cudaMemsetAsync(st->error_dev, 0, sizeof(int32_t), s));
+    reset_counters(*st, s);
+    CUDA_TRY(cudaStreamSynchronize(s));
+    return CPUOPS_B200_STATUS_DEVICE_TIMEOUT;
+  }
+  return 0;
+}
+
+CPUOPS_B200_API int cpuops_b200_set_wait_budget_us(uint32_t microseconds) {
+  if (microseconds == 0) microseconds = kDefaultWaitBudgetUs;
+  g_wait_budget_us.store(microseconds);
+  return 0;
+}
+
+CPUOPS_B200_API int cpuops_b200_selftest_wait_timeout(uint32_t budget_us, void* stream) {
+  if (budget_us == 0 || budget_us > 100000u) {
+    set_error("selftest_wait_timeout: budget must be 1..100000 microseconds");
+    return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
+  }
+  DeviceState* st = nullptr;
+  if (int rc = init_device(-1, &st)) return rc;
+  std::lock_guard<std::mutex> lk(st->mu);
+  cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : st->stream;
+  wait_timeout_probe_kernel<<<1, 32, 0, s>>>(st->error_dev, budget_us);
+  g_launches.fetch_add(1);
+  CUDA_TRY(cudaGetLastError());
   CUDA_TRY(cudaMemcpyAsync(st->error_host, st->error_dev, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
   CUDA_TRY(cudaStreamSynchronize(s));
   if (*st->error_host != 0) {
@@ -314,27 +444,16 @@ CPUOPS_B200_API int cpuops_b200_stream_status(void* stream) {
     CUDA_TRY(cudaStreamSynchronize(s));
     return CPUOPS_B200_STATUS_DEVICE_TIMEOUT;
   }
-  return 0;
-}
-
-// Experiments only, not declared in the public header: {SM cycles, ns} of CTA 0 of the
-// last GEMM kernel when CPUOPS_B200_CLK is set.
-CPUOPS_B200_API int cpuops_b200_debug_clock(unsigned long long* out) {
-  if (!g_clk_buf || !out) return 1;
-  cudaDeviceSynchronize();
-  // [8],[9]: first CTA start / last CTA end (ns)
-  cudaMemcpy(out, g_clk_buf, 16 * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
-  return 0;
+  return CPUOPS_B200_STATUS_SUCCESS;
 }
 
 CPUOPS_B200_API int cpuops_b200_profile(int enable) {
-  std::lock_guard<std::mutex> lk(g_mu);
-  g_profile = enable != 0;
+  g_profile.store(enable != 0);
   return 0;
 }
 
 CPUOPS_B200_API int cpuops_b200_profile_collect(double* total_ms, int32_t* launches) {
-  std::lock_guard<std::mutex> lk(g_mu);
+  std::lock_guard<std::mutex> lk(g_profile_mu);
   double sum = 0.0;
   int n = 0;
   for (auto& pr : g_profile_events) {
@@ -354,15 +473,15 @@ CPUOPS_B200_API int cpuops_b200_profile_collect(double* total_ms, int32_t* launc
 
 }  // extern "C"
 
-// The whole call.  depth 0: a caller's descriptor.  depth 1: one row panel of a
-// host-operand call, issued by depth 0 on one of the panel streams (asynchronous, with
-// host pointers allowed: the parent synchronises).  g_mu is held by the caller.
+// The whole call.  depth 0: a caller's descriptor; takes the device's lock.  depth 1: one
+// row panel of a host-operand call, issued by depth 0 on one of the panel streams
+// (asynchronous, with host pointers allowed: the parent synchronises and holds the lock).
 static int gemm_body(const cpuops_b200_gemm_desc* d, int depth);
 
 extern "C" {
 
 CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* d) {
-  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceRestore restore;  // a call that names another device leaves the caller's current device alone
   return gemm_body(d, 0);
 }
 
@@ -412,12 +531,16 @@ static int run_host_row_panels(const cpuops_b200_gemm_desc* d, DeviceState& st, 
   if (env_switches().panels > 0) n_panels = std::max(2, std::min(env_switches().panels, m / 128));
   const int panel_rows = static_cast<int>(align_up((m + n_panels - 1) / n_panels, 128));
   int issued = 0;
-  for (int row0 = 0; row0 < m; row0 += panel_rows, ++issued) {
+  for (int row0 = 0, rows = 0; row0 < m; row0 += rows, ++issued) {
     const int j = issued % DeviceState::kPanelStreams;
     if (issued < DeviceState::kPanelStreams)
       CUDA_TRY(cudaStreamWaitEvent(st.panel_stream[j], st.fork_event, 0));
     cpuops_b200_gemm_desc pd = sub;
-    pd.m = std::min(panel_rows, m - row0);
+    // a tail of one tile's height or less joins this panel: no panel is ever so short that
+    // it would be launched as a small-m problem with a different plan
+    rows = std::min(panel_rows, m - row0);
+    if (m - row0 - rows <= kTileM) rows = m - row0;
+    pd.m = rows;
     pd.stream = st.panel_stream[j];
     // A: k-major rows of m (row pitch A.pitch bytes), or m contiguous (int8 column-major)
     pd.a = static_cast<const uint8_t*>(d->a) + (a_kmajor ? row0 * A.pitch : static_cast<int64_t>(row0));
@@ -445,6 +568,7 @@ static int run_host_row_panels(const cpuops_b200_gemm_desc* d, DeviceState& st, 
     set_error("device-side bounded wait timed out (code %d)", *st.error_host);
     *st.error_host = 0;
     cudaMemsetAsync(st.error_dev, 0, sizeof(int32_t), stream);
+    reset_counters(st, stream);
     cudaStreamSynchronize(stream);
     return CPUOPS_B200_STATUS_DEVICE_TIMEOUT;
   }
@@ -542,6 +666,11 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
   DeviceState* stp = nullptr;
   if (int rc = init_device(d->device, &stp)) return rc;
   DeviceState& st = *stp;
+  std::unique_lock<std::mutex> device_lock;
+  if (depth == 0) {
+    device_lock = std::unique_lock<std::mutex>(st.mu);
+    t_tm_cache = st.tm_cache;
+  }
   cudaStream_t stream = d->stream ? static_cast<cudaStream_t>(d->stream) : st.stream;
   const bool async = (d->flags & CPUOPS_B200_FLAG_ASYNC) != 0;
 
@@ -585,7 +714,7 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
   const int k_blocks = k > 0 ? (k + elems_per_block - 1) / elems_per_block : 0;
   const int kind = !is_mx ? kKindI8 : (fp4_pair ? kKindMxf4 : kKindMxf8);
   if (k > 0) {
-    ch.swap = (m <= 64 && n > m);
+    ch.swap = (depth == 0 && m <= 64 && n > m);  // (row panels keep their parent's plan)
     const int Mk = ch.swap ? n : m, Nk = ch.swap ? m : n;
     const bool bk_role_mn = !(ch.swap ? a_kmajor : b_kmajor);  // N-side operand is MN-major
     if (d->tile_n > 0) {
@@ -648,6 +777,22 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     ch.pair = legal && want;
   }
 
+  // ---- small-m MX problems take the decode kernel ---------------------------------------------
+  // (one launch, raw scales, every SM streaming an equal share of the weights).  It fetches the
+  // scale rows 16 bytes at a time, which wants 16-byte aligned bases and leading dimensions; a
+  // forced tile width or slice count keeps the general kernel, whose plan those describe.
+  DecodePlan dp;
+  if (k > 0 && is_mx && !mixed && ch.swap && m <= 64 && d->tile_n == 0 && d->split_k_slices <= 1 &&
+      !(d->flags & (CPUOPS_B200_FLAG_PAIR_ON | CPUOPS_B200_FLAG_PAIR_OFF)) && !env_switches().no_decode &&
+      (n + kTileM - 1) / kTileM <= kDecodeMaxTiles) {
+    auto scales_ok = [](const void* ptr, bool on_device, int ld, int rows) {
+      return (!on_device || (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0) && (rows <= 1 || ld % 16 == 0);
+    };
+    if (scales_ok(d->a_scales, sa_dev, d->ld_scales_a, m) && scales_ok(d->b_scales, sb_dev, d->ld_scales_b, n))
+      dp = plan_decode(st, kind, n, m, k_blocks, d->split_k_slices == 1,
+                       (d->flags & CPUOPS_B200_FLAG_B_IMMUTABLE) != 0);
+  }
+
   if (depth == 0 && k > 0 && !a_dev && !d_dev && !ch.swap && ch.slices == 1 && m >= 1024)
     return run_host_row_panels(d, st, stream, ch, A, B, is_mx, fp4_b, a_kmajor, b_dev, sb_dev, c_rm);
 
@@ -655,7 +800,7 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
   Plan plan;
   const int64_t c_outer = c_rm ? m : n, c_inner = c_rm ? n : m;
   size_t off_a = 0, off_b = 0, off_sa = 0, off_sb = 0, off_c = 0, off_d = 0, off_sfa = 0, off_sfb = 0,
-         off_ws = 0, off_ops[CPUOPS_B200_MAX_OPS] = {0};
+         off_ws = 0, off_partial = 0, off_ops[CPUOPS_B200_MAX_OPS] = {0};
   int64_t a_pitch_dev = A.pitch, b_pitch_dev = B.pitch;
   bool a_repack = false, b_repack = false;
   const bool a_mask = fp4_a && (k & 1), b_mask = fp4_b && (k & 1);
@@ -709,7 +854,9 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
   if (k > 0) {
     Mk = ch.swap ? n : m;
     Nk = ch.swap ? m : n;
-    if (is_mx) {
+    if (dp.use) {
+      if (dp.partial_bytes) off_partial = plan.take(dp.partial_bytes);
+    } else if (is_mx) {
       bps = fp4_pair ? 8 : 4;
       // a pair always reads the scales of both of its 128-row halves
       sfa_bytes = cpuops_b200_scale_layout_bytes(ch.pair ? static_cast<int>(align_up(Mk, 256)) : Mk, k,
@@ -718,7 +865,7 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
       off_sfa = plan.take(sfa_bytes);
       off_sfb = plan.take(sfb_bytes);
     }
-    if (ch.slices > 1) off_ws = plan.take(static_cast<size_t>(ch.slices) * Mk * Nk * 4);
+    if (ch.slices > 1 && !dp.use) off_ws = plan.take(static_cast<size_t>(ch.slices) * Mk * Nk * 4);
   }
   uint8_t* wsp = nullptr;
   if (plan.total > 0) {
@@ -846,6 +993,104 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     }
     g_launches.fetch_add(1);
     CUDA_TRY(cudaGetLastError());
+  } else if (dp.use) {
+    // ---- decode kernel: W = the caller's B on the MMA M side, X = the caller's A ---------------
+    CUtensorMap tmW, tmX;
+    if (int rc = make_tensor_map(&tmW, b_ptr, B.inner_bytes, B.outer, b_pitch_dev, 128)) return rc;
+    // X: a box of exactly its m rows (rows outside the tensor would cost TMA time each)
+    if (int rc = make_tensor_map(&tmX, a_ptr, A.inner_bytes, A.outer, a_pitch_dev, static_cast<uint32_t>(m)))
+      return rc;
+    DecodeParams q;
+    memset(&q, 0, sizeof(q));
+    q.Mk = n;
+    q.Nk = m;
+    q.kblocks32 = (k + 31) / 32;
+    q.ld_sw = d->ld_scales_b;
+    q.ld_sx = d->ld_scales_a;
+    q.sw = sb_ptr;
+    q.sx = sa_ptr;
+    q.w_early = dp.w_early;
+    q.tiles = dp.tiles;
+    q.k_blocks = k_blocks;
+    q.BN = dp.BN;
+    q.stages = dp.stages;
+    q.tile_aligned = dp.tile_aligned;
+    q.max_pieces = dp.max_pieces;
+    q.tmem_cols = dp.tmem_cols;
+    if (kind == kKindMxf4) {
+      q.idesc = make_idesc_block_scaled(1u, 1u, kTileM, dp.BN);  // e2m1 x e2m1
+    } else {
+      auto code = [](int f) { return f == CPUOPS_B200_FMT_E5M2 ? 1u : 0u; };
+      q.idesc = make_idesc_block_scaled(code(d->b_format), code(d->a_format), kTileM, dp.BN);
+    }
+    q.wait_budget_us = g_wait_budget_us.load();
+    q.epi = epi;
+    q.partial = reinterpret_cast<float*>(wsp + off_partial);
+    if (int rc = ensure_counters(st, stream, &q.counters)) return rc;
+    q.error = st.error_dev;
+#ifdef CPUOPS_B200_INSTRUMENT
+    if (env_switches().clk) {
+      // sixteen launches' worth of stamps, one block of 16 words per launch in turn; the
+      // buffer is cleared when it is read (cpuops_b200_debug_decode_clock), never between
+      // launches, so that consecutive launches stay adjacent in the stream
+      if (!g_decode_clk) {
+        cudaMalloc(&g_decode_clk, 16 * 16 * sizeof(unsigned long long));
+        cudaMemset(g_decode_clk, 0, 16 * 16 * sizeof(unsigned long long));
+      }
+      q.clk = g_decode_clk + 16 * (g_decode_clk_launch++ % 16);
+      static bool told = false;
+      if (!told) {
+        told = true;
+        int per_sm = 0;
+        if (kind == kKindMxf4) {
+          cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_mx_kernel<kKindMxf4>, kDecodeThreads, dp.smem);
+        } else {
+          cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_mx_kernel<kKindMxf8>, kDecodeThreads, dp.smem);
+        }
+        fprintf(stderr, "[instrument] decode kernel: %d bytes of shared memory, %d CTAs per SM can be resident\n",
+                dp.smem, per_sm);
+      }
+    }
+#endif
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(dp.grid));
+    cfg.blockDim = dim3(kDecodeThreads);
+    cfg.dynamicSmemBytes = static_cast<size_t>(dp.smem);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    // The kernel may start while the kernel before it in the stream is finishing; every
+    // role waits for that kernel before it touches memory (see decode_kernel.cuh).
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    const bool profile = g_profile.load();
+    if (profile) {
+      CUDA_TRY(cudaEventCreate(&ev0));
+      CUDA_TRY(cudaEventCreate(&ev1));
+      CUDA_TRY(cudaEventRecord(ev0, stream));
+    }
+    g_last_plan = cpuops_b200_plan{};
+    g_last_plan.swapped = 1;
+    g_last_plan.tile_n = dp.BN;
+    g_last_plan.slices = dp.max_pieces;
+    g_last_plan.stages = dp.stages;
+    g_last_plan.grid = dp.grid;
+    g_last_plan.epilogue_warps = 4;
+    g_last_plan.decode = 1;
+    if (kind == kKindMxf4) {
+      CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_mx_kernel<kKindMxf4>, tmW, tmX, q));
+    } else {
+      CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_mx_kernel<kKindMxf8>, tmW, tmX, q));
+    }
+    g_launches.fetch_add(1);
+    CUDA_TRY(cudaGetLastError());
+    if (profile) {
+      CUDA_TRY(cudaEventRecord(ev1, stream));
+      std::lock_guard<std::mutex> plk(g_profile_mu);
+      g_profile_events.emplace_back(ev0, ev1);
+    }
   } else {
     // ---- scales -> tile-ordered layout (MX) ------------------------------------------------
     const uint8_t* sfa_dev = nullptr;  // tile-ordered scale atoms of the kernel-view A / B side
@@ -871,6 +1116,7 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
       sfb_dev = wsp + off_sfb;
       // The caller's B scales (kernel-view A side when the operands are swapped): use the
       // kept copy when B was registered with cpuops_b200_prepare_b, building it on first use.
+      std::lock_guard<std::mutex> registry_lock(g_registry_mu);
       PreparedB* pb = sb_dev ? find_prepared(st.device, d->b_scales, n, k, d->ld_scales_b) : nullptr;
       if (pb) {
         const ScaleLayout& L = swap ? La : Lb;
@@ -1019,7 +1265,8 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
       if (env_switches().epi_warps == 8 || env_switches().epi_warps == 4) epi_warps = env_switches().epi_warps;
     }
     p.error = st.error_dev;
-    p.debug_flags = env_switches().debug_flags;
+    p.wait_budget_us = g_wait_budget_us.load();
+#ifdef CPUOPS_B200_INSTRUMENT
     if (env_switches().clk) {
       if (!g_clk_buf) cudaMalloc(&g_clk_buf, 128);
       cudaMemsetAsync(g_clk_buf + 8, 0xFF, 8, stream);
@@ -1027,6 +1274,7 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
       cudaMemsetAsync(g_clk_buf + 12, 0xFF, 8, stream);  // [12]: first CTA entry (ns)
       p.clk_dbg = g_clk_buf;
     }
+#endif
     const int sf_stage_bytes = p.sfa_stage_bytes + p.sfb_stage_bytes;
     const int per_stage = gemm_stage_bytes(b_rows) + sf_stage_bytes;
     int stages = (st.smem_optin - 1024 - kBarrierBytes - (p.ring_bufs ? 1024 + ring_bytes(p.ring_bufs, epi_warps) : 0)) /
@@ -1088,12 +1336,13 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     }
     cfg.gridDim = dim3(grid);
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
-    if (g_profile) {
+    const bool profile = g_profile.load();
+    if (profile) {
       CUDA_TRY(cudaEventCreate(&ev0));
       CUDA_TRY(cudaEventCreate(&ev1));
       CUDA_TRY(cudaEventRecord(ev0, stream));
     }
-    if (is_mx && !g_profile) {
+    if (is_mx && !profile) {
       // MX: the scale re-layout kernel is the launch just before this one.  Programmatic
       // stream serialization lets this kernel's CTAs start (barriers, tensor memory,
       // descriptor prefetch) while that one is still running; the producer thread waits
@@ -1103,6 +1352,7 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
       attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
       ++n_attr;
     }
+    g_last_plan = cpuops_b200_plan{};
     g_last_plan.swapped = ch.swap ? 1 : 0;
     g_last_plan.tile_n = ch.BN;
     g_last_plan.pair = ch.pair ? 1 : 0;
@@ -1136,8 +1386,9 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     }
     g_launches.fetch_add(1);
     CUDA_TRY(cudaGetLastError());
-    if (g_profile) {
+    if (profile) {
       CUDA_TRY(cudaEventRecord(ev1, stream));
+      std::lock_guard<std::mutex> plk(g_profile_mu);
       g_profile_events.emplace_back(ev0, ev1);
     }
     if (ch.slices > 1) {
@@ -1166,6 +1417,7 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     set_error("device-side bounded wait timed out (code %d)", *st.error_host);
     *st.error_host = 0;
     cudaMemsetAsync(st.error_dev, 0, sizeof(int32_t), stream);
+    reset_counters(st, stream);
     cudaStreamSynchronize(stream);
     return CPUOPS_B200_STATUS_DEVICE_TIMEOUT;
   }
@@ -1225,15 +1477,18 @@ int noalloc_setup(int device, NoAllocDevice** out) {
     CUDA_TRY(cudaDeviceGetAttribute(&nd.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
     CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<kKindI8, false>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, nd.smem_optin));
-    if (!g_encode) {
-      void* fn = nullptr;
-      cudaDriverEntryPointQueryResult qres;
-      CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
-      if (!fn || qres != cudaDriverEntryPointSuccess) {
-        set_error("cuTensorMapEncodeTiled is not exported by this driver");
-        return CPUOPS_B200_STATUS_CUDA_ERROR;
+    {
+      std::lock_guard<std::mutex> reg(g_registry_mu);
+      if (!g_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+        if (!fn || qres != cudaDriverEntryPointSuccess) {
+          set_error("cuTensorMapEncodeTiled is not exported by this driver");
+          return CPUOPS_B200_STATUS_CUDA_ERROR;
+        }
+        g_encode = reinterpret_cast<EncodeTiledFn>(fn);
       }
-      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
     }
     nd.ready = true;
   }
@@ -1278,11 +1533,11 @@ CPUOPS_B200_API int cpuops_b200_gemm_i8_noalloc(const cpuops_b200_gemm_desc* d) 
     if (oc >= CPUOPS_B200_OP_BIAS_ADD && !d->ops[t].ptr) return CPUOPS_B200_STATUS_INVALID_ARGUMENTS;
   }
 
-  std::lock_guard<std::mutex> lk(g_mu);
   if (probe_devices() <= 0) {
     set_error("no sm_100 CUDA device is available; this library has no CPU fallback");
     return CPUOPS_B200_STATUS_NO_DEVICE;
   }
+  DeviceRestore restore;
   int device = d->device;
   if (device < 0) {
     CUDA_TRY(cudaGetDevice(&device));
@@ -1290,6 +1545,9 @@ CPUOPS_B200_API int cpuops_b200_gemm_i8_noalloc(const cpuops_b200_gemm_desc* d) 
     CUDA_TRY(cudaSetDevice(device));
   }
   if (device >= 64) return CPUOPS_B200_STATUS_BAD_DESCRIPTOR;
+  // the device's lock: calls share the scratch array, so they must not overlap
+  std::lock_guard<std::mutex> lk(g_dev[device].mu);
+  t_tm_cache = g_dev[device].tm_cache;
   NoAllocDevice* nd = nullptr;
   if (int rc = noalloc_setup(device, &nd)) return rc;
   // NULL means the legacy default stream here: creating a stream would be an allocation.
@@ -1314,6 +1572,11 @@ CPUOPS_B200_API int cpuops_b200_gemm_i8_noalloc(const cpuops_b200_gemm_desc* d) 
   const int k_blocks = (k + 127) / 128;
   int slices = d->split_k_slices > 0 ? d->split_k_slices : std::min(8, k_blocks);
   slices = std::max(1, std::min(slices, k_blocks));
+  if (d->split_k_slices <= 0) {
+    // automatic: as many slices (up to 8) as the array has room for, at least one
+    const size_t fit = CPUOPS_B200_NOALLOC_SCRATCH_BYTES / (static_cast<size_t>(m) * n * 4);
+    slices = static_cast<int>(std::max<size_t>(1, std::min<size_t>(static_cast<size_t>(slices), fit)));
+  }
   const size_t need = static_cast<size_t>(slices) * m * n * 4;
   if (need > CPUOPS_B200_NOALLOC_SCRATCH_BYTES) {
     set_error("gemm_i8_noalloc: %d slices of a %d x %d s32 result need %zu bytes of scratch; the "
@@ -1387,6 +1650,7 @@ CPUOPS_B200_API int cpuops_b200_gemm_i8_noalloc(const cpuops_b200_gemm_desc* d) 
     p.ws_sc = 1;
   }
   p.error = error_word;
+  p.wait_budget_us = g_wait_budget_us.load();
   const int per_stage = gemm_stage_bytes(BN);
   int stages = std::min({(nd->smem_optin - 1024 - kBarrierBytes) / per_stage, kMaxStages, std::max(2, k_blocks)});
   p.stages = stages;

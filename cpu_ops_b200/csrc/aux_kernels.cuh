@@ -8,8 +8,27 @@
 
 #include "epilogue.cuh"
 #include "gemm_params.h"
+#include "ptx_sm100.cuh"
 
 namespace b200 {
+
+// Self-test of the bounded-wait path: one warp waits, with the given budget, on an mbarrier
+// that nothing ever arrives on.  The wait gives up when the budget is spent, the warp
+// records kErrProducerWait in the device error word exactly as the GEMM kernels' roles do,
+// and the kernel returns normally: nothing hangs, traps or faults.
+__global__ void wait_timeout_probe_kernel(int32_t* error, uint32_t budget_us) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int abort_flag;
+  const uint32_t bar_addr = smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(bar_addr, 1);
+    fence_mbar_init();
+  }
+  __syncwarp();
+  const bool done = mbar_wait_bounded(bar_addr, 0, &abort_flag, static_cast<uint64_t>(budget_us) * 1000ull);
+  if (!__all_sync(0xffffffffu, done) && threadIdx.x == 0) atomicCAS(error, 0, kErrProducerWait);
+}
 
 // Scale layout consumed by tcgen05.cp (32x128b.warpx4) + block-scaled MMAs.
 // The CPU library reads scales[row*ld + kk/32] directly while packing

@@ -28,6 +28,14 @@
 #include "ptx_sm100.cuh"
 #include "ptx_sm100_pair.cuh"
 
+// Per-role cycle counters of CTA 0 exist only in a build with -DCPUOPS_B200_INSTRUMENT; in
+// the product build the pointer is a constant null and the compiler drops every use of it.
+#ifdef CPUOPS_B200_INSTRUMENT
+#define B200_CLK(p) ((p).clk_dbg)
+#else
+#define B200_CLK(p) (static_cast<unsigned long long*>(nullptr))
+#endif
+
 namespace b200 {
 
 constexpr int kGemmThreads = 192;      // producer, MMA issuer, 4 epilogue warps
@@ -193,7 +201,8 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
   const uint32_t smem_base = raw_addr + pad;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (p.clk_dbg != nullptr && threadIdx.x == 0) atomicMin(p.clk_dbg + 12, global_timer_ns());
+  const uint64_t budget_ns = static_cast<uint64_t>(p.wait_budget_us) * 1000ull;
+  if (B200_CLK(p) != nullptr && threadIdx.x == 0) atomicMin(B200_CLK(p) + 12, global_timer_ns());
   const int stages = p.stages;
   const int b_rows = p.BN / kCtas;  // rows of the B tile staged by this CTA
   const int stage_bytes = gemm_stage_bytes(b_rows);
@@ -278,8 +287,8 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
   const uint64_t sf_hi64 = make_smem_desc_hi(0, 128, 0);  // 32 rows x 16 B, 8-row groups 128 B apart
   long long dbg_c0 = 0;
   uint64_t dbg_t0 = 0;
-  if (p.clk_dbg != nullptr && threadIdx.x == 0) atomicMin(p.clk_dbg + 8, global_timer_ns());
-  if (p.clk_dbg != nullptr && blockIdx.x == 0 && threadIdx.x == 64) {
+  if (B200_CLK(p) != nullptr && threadIdx.x == 0) atomicMin(B200_CLK(p) + 8, global_timer_ns());
+  if (B200_CLK(p) != nullptr && blockIdx.x == 0 && threadIdx.x == 64) {
     dbg_c0 = clock64();
     dbg_t0 = global_timer_ns();
   }
@@ -305,7 +314,7 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
       // The scale atoms come from the re-layout kernel launched just before this one,
       // which may still be running (programmatic stream serialization).
       if constexpr (kMx) asm volatile("griddepcontrol.wait;" ::: "memory");
-      const bool pdbg = p.clk_dbg != nullptr && blockIdx.x == 0;
+      const bool pdbg = B200_CLK(p) != nullptr && blockIdx.x == 0;
       long long pdbg_wait = 0;
       const long long pdbg_start = pdbg ? clock64() : 0;
       for (int t = work0; t < total_tiles && ok; t += work_step) {
@@ -323,7 +332,7 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
         }
         for (int i = 0; i < tc.nkb; ++i, kx += 128) {
           const long long pw0 = pdbg ? clock64() : 0;
-          if (!peek && !__all_sync(0xffffffffu, mbar_wait_bounded(empty_addr, ph ^ 1u, abort_flag))) {
+          if (!peek && !__all_sync(0xffffffffu, mbar_wait_bounded(empty_addr, ph ^ 1u, abort_flag, budget_ns))) {
             if (el) record_error(p, abort_flag, kErrProducerWait);
             ok = false;
             break;
@@ -381,14 +390,14 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
         }
       }
       if (pdbg && el) {
-        p.clk_dbg[10] = static_cast<unsigned long long>(clock64() - pdbg_start);
-        p.clk_dbg[11] = static_cast<unsigned long long>(pdbg_wait);
+        B200_CLK(p)[10] = static_cast<unsigned long long>(clock64() - pdbg_start);
+        B200_CLK(p)[11] = static_cast<unsigned long long>(pdbg_wait);
       }
       if (*abort_flag != 0 && el) {
         // Let copies that were already issued land before the CTA exits.
         int dummy = 0;
         for (int st = 0; st < stages; ++st)
-          if (armed & (1u << st)) mbar_wait_bounded(full_bar(st), (armed_parity >> st) & 1u, &dummy);
+          if (armed & (1u << st)) mbar_wait_bounded(full_bar(st), (armed_parity >> st) & 1u, &dummy, budget_ns);
         if constexpr (kPair) {
           // the peer cannot watch the leader's barriers: give its copies time to land
           if (!leader) {
@@ -446,7 +455,7 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
       const uint32_t sfa_half = 4u, sfb_half = 2u * sfb_atoms;  // mxf4: second 4-block atom row
       const uint32_t full0 = full_bar(0), empty0 = empty_bar(0);
 
-      const bool dbg = p.clk_dbg != nullptr && blockIdx.x == 0;
+      const bool dbg = B200_CLK(p) != nullptr && blockIdx.x == 0;
       long long dbg_wait_acc = 0, dbg_wait_full = 0;
       const long long dbg_start = dbg ? clock64() : 0;
       int s = 0, buf = 0;
@@ -455,7 +464,7 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
       for (int t = work0; t < total_tiles && ok; t += work_step) {
         const TileCoord tc = decode_tile(p, t, work_step);
         long long tw0 = dbg ? clock64() : 0;
-        if (!__all_sync(kAll, mbar_wait_bounded(acc_empty_bar(buf), acc_ph ^ 1u, abort_flag))) {
+        if (!__all_sync(kAll, mbar_wait_bounded(acc_empty_bar(buf), acc_ph ^ 1u, abort_flag, budget_ns))) {
           if (el) record_error(p, abort_flag, kErrMmaWaitAcc);
           break;
         }
@@ -466,7 +475,7 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
         uint32_t accumulate = 0;
         for (int i = 0; i < tc.nkb; ++i) {
           tw0 = dbg ? clock64() : 0;
-          if (!peek && !__all_sync(kAll, mbar_wait_bounded(full_addr, ph, abort_flag))) {
+          if (!peek && !__all_sync(kAll, mbar_wait_bounded(full_addr, ph, abort_flag, budget_ns))) {
             if (el) record_error(p, abort_flag, kErrMmaWaitFull);
             ok = false;
             break;
@@ -535,13 +544,13 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
       // Nothing may still be executing when tensor memory is released.
       tc_commit_g<kPair>(drain_bar, el);
       int dummy = 0;
-      if (!__all_sync(kAll, mbar_wait_bounded(drain_bar, 0, &dummy)) && el)
+      if (!__all_sync(kAll, mbar_wait_bounded(drain_bar, 0, &dummy, budget_ns)) && el)
         record_error(p, abort_flag, kErrDrainWait);
       if (dbg && el) {
-        p.clk_dbg[2] = static_cast<unsigned long long>(clock64() - dbg_start);
-        p.clk_dbg[3] = static_cast<unsigned long long>(dbg_wait_full);
-        p.clk_dbg[4] = static_cast<unsigned long long>(dbg_wait_acc);
-        p.clk_dbg[7] = 0;
+        B200_CLK(p)[2] = static_cast<unsigned long long>(clock64() - dbg_start);
+        B200_CLK(p)[3] = static_cast<unsigned long long>(dbg_wait_full);
+        B200_CLK(p)[4] = static_cast<unsigned long long>(dbg_wait_acc);
+        B200_CLK(p)[7] = 0;
       }
     }
     __syncwarp();
@@ -565,7 +574,7 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
     uint32_t cq_b = 0, cq_ph = 0;  // its buffer and that buffer's barrier parity
     uint32_t cissued = 0, ci_b = 0;  // C chunks requested so far, buffer of the next request
     bool alive = true;
-    const bool edbg = p.clk_dbg != nullptr && blockIdx.x == 0 && warp == 2 && lane == 0;
+    const bool edbg = B200_CLK(p) != nullptr && blockIdx.x == 0 && warp == 2 && lane == 0;
     long long edbg_wait = 0;
     const long long edbg_start = edbg ? clock64() : 0;
     // pair: the leader's MMA thread waits for the epilogue warps of both CTAs
@@ -590,7 +599,7 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
         for (int c = c0; c < c0 + 2 * cstep && c < nchunks; c += cstep) request_c(n0 + c * 32, row0);
       }
       const long long te0 = edbg ? clock64() : 0;
-      const bool ready = mbar_wait_bounded(acc_full_bar(buf), acc_ph, abort_flag);
+      const bool ready = mbar_wait_bounded(acc_full_bar(buf), acc_ph, abort_flag, budget_ns);
       if (!__all_sync(0xffffffffu, ready)) {
         if (lane == 0) record_error(p, abort_flag, kErrEpilogueWait);
         alive = false;
@@ -630,7 +639,7 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
         const int kcol0 = n0 + c * 32;
         uint32_t c_row = 0, d_row = 0;  // shared-memory addresses of this lane's row
         if (ring) {
-          const bool got = mbar_wait_bounded(c_full_bar(ew, cq_b), cq_ph, abort_flag);
+          const bool got = mbar_wait_bounded(c_full_bar(ew, cq_b), cq_ph, abort_flag, budget_ns);
           if (!__all_sync(0xffffffffu, got)) {
             if (lane == 0) record_error(p, abort_flag, kErrEpilogueWait);
             alive = false;
@@ -645,7 +654,7 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
           __syncwarp();
         }
         if (d_tma) d_row = my_c + cq_b * 4096u + static_cast<uint32_t>(lane) * 128u;
-        if (krow < p.Mk && kcol0 < p.Nk && !(p.debug_flags & 4))
+        if (krow < p.Mk && kcol0 < p.Nk)
           store_chunk<kInt>(p, r, krow, kcol0, tc.slice, c_row, d_row, lane & 7);
         if (d_tma) {
           fence_proxy_async_shared_cta();  // this lane's row -> visible to the TMA store
@@ -675,14 +684,14 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
     }
     if (d_tma && lane == 0) bulk_wait_group_all();  // D is complete before the kernel ends
     if (edbg) {
-      p.clk_dbg[5] = static_cast<unsigned long long>(clock64() - edbg_start);
-      p.clk_dbg[6] = static_cast<unsigned long long>(edbg_wait);
+      B200_CLK(p)[5] = static_cast<unsigned long long>(clock64() - edbg_start);
+      B200_CLK(p)[6] = static_cast<unsigned long long>(edbg_wait);
     }
     if (ring && *abort_flag != 0 && lane == 0) {
       // let C chunks that were requested but never consumed land before the CTA exits
       int dummy = 0;
       for (; cq < cissued; ++cq) {
-        mbar_wait_bounded(c_full_bar(ew, cq_b), cq_ph, &dummy);
+        mbar_wait_bounded(c_full_bar(ew, cq_b), cq_ph, &dummy, budget_ns);
         if (++cq_b == nb) {
           cq_b = 0;
           cq_ph ^= 1u;
@@ -691,9 +700,9 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
     }
   }
 
-  if (p.clk_dbg != nullptr && blockIdx.x == 0 && threadIdx.x == 64) {
-    p.clk_dbg[0] = static_cast<unsigned long long>(clock64() - dbg_c0);
-    p.clk_dbg[1] = global_timer_ns() - dbg_t0;
+  if (B200_CLK(p) != nullptr && blockIdx.x == 0 && threadIdx.x == 64) {
+    B200_CLK(p)[0] = static_cast<unsigned long long>(clock64() - dbg_c0);
+    B200_CLK(p)[1] = global_timer_ns() - dbg_t0;
   }
   tc_fence_before_sync();
   if constexpr (kPair) {
@@ -704,7 +713,7 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
     __syncthreads();
   }
   if (warp == 1) tmem_dealloc_g<kPair>(tmem_base, kTmemCols);
-  if (p.clk_dbg != nullptr && threadIdx.x == 0) atomicMax(p.clk_dbg + 9, global_timer_ns());
+  if (B200_CLK(p) != nullptr && threadIdx.x == 0) atomicMax(B200_CLK(p) + 9, global_timer_ns());
 }
 
 }  // namespace b200

@@ -80,8 +80,10 @@ struct GemmParams {
   int32_t ring_bufs;        // ring buffers per epilogue warp: 0 (no ring) or 2
   int32_t tx_operand_bytes; // bytes the A and B loads of one stage credit to the barrier, per CTA
   int32_t* error;           // device error word
-  int32_t debug_flags;      // experiments only (CPUOPS_B200_DEBUG)
-  unsigned long long* clk_dbg;  // experiments only: {SM cycles, nanoseconds} of CTA 0
+  uint32_t wait_budget_us;  // budget of every bounded device-side wait
+#ifdef CPUOPS_B200_INSTRUMENT
+  unsigned long long* clk_dbg;  // instrumented build: {SM cycles, nanoseconds} of CTA 0
+#endif
 };
 
 // Width at which the last tile column of an n extent is computed when it is computed

@@ -81,19 +81,21 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
-// Bounded wait.  Returns false when the phase did not complete within the
-// time budget (or another role already flagged an abort); the caller then
-// records an error and unwinds.  `abort_flag` lives in shared memory.
-constexpr uint64_t kWaitBudgetNs = 1000000000ull;  // 1 s: far above any legitimate wait
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
-                                                  volatile int* abort_flag) {
+// Bounded wait.  Returns false when the phase did not complete within `budget_ns` (or
+// another role already flagged an abort); the caller then records an error and unwinds.
+// `abort_flag` lives in shared memory.  The launcher passes the budget (default 1 s: far
+// above any legitimate wait, yet short enough that a lost arrival ends as an error code
+// instead of a hung device).
+constexpr uint32_t kDefaultWaitBudgetUs = 1000000u;
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                  uint64_t budget_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 0x3FF) == 0) {
+    if ((++spins & 0xFF) == 0) {
       if (*abort_flag != 0) return false;
-      if (global_timer_ns() - t0 > kWaitBudgetNs) return false;
+      if (global_timer_ns() - t0 > budget_ns) return false;
     }
     if (spins > 0x40000000u) return false;  // hard iteration cap
   }

@@ -9,31 +9,15 @@ namespace {
 
 // ---- tensor maps --------------------------------------------------------------
 
-// A tensor map is a pure function of its encode arguments, and a caller that repeats
-// a GEMM on the same buffers (a decode loop) asks for the same few maps again and
-// again: a small direct-mapped cache saves the driver call (about a microsecond each).
-// Guarded by g_mu like the rest of the call.
-struct TensorMapKey {
-  uint64_t base, d0, d1, pitch;
-  uint32_t box1, words;
-  bool operator==(const TensorMapKey& o) const {
-    return base == o.base && d0 == o.d0 && d1 == o.d1 && pitch == o.pitch && box1 == o.box1 &&
-           words == o.words;
-  }
-};
-struct TensorMapSlot {
-  bool valid = false;
-  TensorMapKey key;
-  CUtensorMap map;
-};
-constexpr int kTensorMapSlots = 64;
-TensorMapSlot g_tm_cache[kTensorMapSlots];
+// The cache consulted below belongs to the device whose lock the calling thread holds;
+// the entry points point this at it (DeviceState::tm_cache) before building maps.
+thread_local TensorMapSlot* t_tm_cache = nullptr;
 
 TensorMapSlot& tensor_map_slot(const TensorMapKey& k) {
   uint64_t h = k.base * 0x9E3779B97F4A7C15ull;
   h ^= (k.d0 + 0x632BE59BD9B4E019ull) * 0xC2B2AE3D27D4EB4Full;
   h ^= (k.d1 * 31 + k.pitch * 17 + k.box1 * 7 + k.words) * 0x165667B19E3779F9ull;
-  return g_tm_cache[(h >> 32) % kTensorMapSlots];
+  return t_tm_cache[(h >> 32) % kTensorMapSlots];
 }
 
 // 2-D byte tensor: `inner` contiguous bytes per row, `outer` rows `pitch` bytes

@@ -7,6 +7,8 @@
 #ifndef CPU_OPS_B200_MX_TYPES_H_
 #define CPU_OPS_B200_MX_TYPES_H_
 
+#include <algorithm>
+#include <array>
 #include <cmath>
 #include <cstdint>
 #include <cstring>
@@ -51,7 +53,23 @@ inline unsigned encode_minifloat_rne(float ax, int mbits, int bias) {
   return (static_cast<unsigned>(expo) << mbits) | (q - (1u << mbits));
 }
 
+// Decode table of a storage type, filled from its to_float (the reference keeps constexpr
+// tables, mx_formats.h:30-102; callers and its tests use them as T::kLut[code] and
+// T::kLut.size()).
+template <typename T, size_t N>
+inline std::array<float, N> make_decode_table() {
+  std::array<float, N> t{};
+  for (size_t c = 0; c < N; ++c) t[c] = T::to_float(static_cast<uint8_t>(c));
+  return t;
+}
+
 }  // namespace b200_detail
+
+// Declared because the reference's umbrella header exports the name (callers write
+// `using cpu_ops::bfloat16_t;`); no operator of this library takes it.
+struct bfloat16_t {
+  uint16_t bits = 0;
+};
 
 // 1-4-3, bias 7, no infinity; S.1111.111 is NaN.
 struct fp8e4m3_t {
@@ -76,7 +94,9 @@ struct fp8e4m3_t {
     if (code > 0x7E) code = 0x7E;
     return static_cast<uint8_t>(sign | code);
   }
+  static const std::array<float, 256> kLut;  // kLut[code] == to_float(code)
 };
+inline const std::array<float, 256> fp8e4m3_t::kLut = b200_detail::make_decode_table<fp8e4m3_t, 256>();
 
 // 1-5-2, bias 15, IEEE-like infinities and NaNs.
 struct fp8e5m2_t {
@@ -105,7 +125,9 @@ struct fp8e5m2_t {
     if (code > 0x7C) code = 0x7C;
     return static_cast<uint8_t>(sign | code);
   }
+  static const std::array<float, 256> kLut;
 };
+inline const std::array<float, 256> fp8e5m2_t::kLut = b200_detail::make_decode_table<fp8e5m2_t, 256>();
 
 // 1-2-1, bias 1: +-{0, .5, 1, 1.5, 2, 3, 4, 6}.  Nibble-level helpers only; two
 // elements share a byte, the even element index in the low nibble.
@@ -123,7 +145,9 @@ struct fp4e2m1_t {
     if (code > 7) code = 7;
     return static_cast<uint8_t>(sign | code);
   }
+  static const std::array<float, 16> kLut;
 };
+inline const std::array<float, 16> fp4e2m1_t::kLut = b200_detail::make_decode_table<fp4e2m1_t, 16>();
 
 // E8M0 block scale: 2^(e - 127); e == 0 is 2^-127, 0xFF is NaN.
 inline float e8m0_to_float(uint8_t e) {
@@ -154,6 +178,34 @@ struct MxTensorRef {
   int ld = 0;         // leading dimension in elements
   int ld_scales = 0;  // leading dimension in scale entries
 };
+
+namespace mma {
+namespace mxvnni_detail {
+
+// Host-side helper of the reference's lossy MX-VNNI policy
+// (gemm/threadblock/mma_policy_mx_vnni.h:55-78), kept because callers and the reference's
+// tests build their own expected values with it: re-quantises up to 32 unscaled values to
+// int8 codes on the grid 2^qexp, qexp = floor(log2(max |v|)) - 6, round to nearest even,
+// clamped to [-128, 127]; q[len..32) is zero; returns qexp (-127 for an all-zero block).
+// The GEMMs of this library never re-quantise: MxVnniPolicy forwards to the exact path.
+inline int quantize_block_i8(const float* v, int len, int8_t* q) {
+  float peak = 0.0f;
+  for (int t = 0; t < len; ++t) peak = std::max(peak, std::fabs(v[t]));
+  std::fill(q, q + 32, static_cast<int8_t>(0));
+  if (peak == 0.0f) return -127;
+  const int qexp = static_cast<int>((b200_detail::f32_to_bits(peak) >> 23) & 0xFF) - 127 - 6;
+  const uint32_t inv_bits = static_cast<uint32_t>(127 - qexp) << 23;  // 2^-qexp
+  float inv;
+  std::memcpy(&inv, &inv_bits, sizeof inv);
+  for (int t = 0; t < len; ++t) {
+    const float code = std::nearbyint(v[t] * inv);  // default rounding mode: nearest even
+    q[t] = static_cast<int8_t>(code > 127.0f ? 127 : (code < -128.0f ? -128 : static_cast<int>(code)));
+  }
+  return qexp;
+}
+
+}  // namespace mxvnni_detail
+}  // namespace mma
 
 }  // namespace cpu_ops
 

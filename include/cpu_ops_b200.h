@@ -89,6 +89,12 @@ enum { CPUOPS_B200_MEM_AUTO = 0, CPUOPS_B200_MEM_HOST = 1, CPUOPS_B200_MEM_DEVIC
  * of two CTAs per 256-row tile).  Neither flag: the library decides by problem size. */
 #define CPUOPS_B200_FLAG_PAIR_ON 2u
 #define CPUOPS_B200_FLAG_PAIR_OFF 4u
+/* The caller promises that B and its scales are not being written by any work still in
+ * flight when this call is enqueued (the weights of a decode loop).  The small-m MX kernel
+ * may then load its first tiles of B while the kernel before it in the stream is still
+ * running; A, C and D keep ordinary stream order.  Without the flag every load waits for
+ * that kernel.  Ignored by the other kernels. */
+#define CPUOPS_B200_FLAG_B_IMMUTABLE 8u
 
 typedef union cpuops_b200_scalar {
   int32_t i32; /* int8 path: alpha/beta/clamp bounds are s32 */
@@ -150,7 +156,14 @@ typedef struct cpuops_b200_gemm_desc {
 /* Replaces Gemm::operator() / GemmMx::operator() (gemm.h:99-127,
  * gemm_mx.h:78-118): validates in the reference's order, runs the GEMM on the
  * GPU, returns a CPUOPS_B200_STATUS_* code.  Synchronous unless FLAG_ASYNC.
- * Thread-safe. */
+ * Thread-safe: calls on the same device are serialised (as the reference serialises
+ * on its thread pool, thread_pool.h:93-96), calls on different devices run side by
+ * side.  The calling thread's current CUDA device is left as it was.
+ * Asynchronous calls are plain kernel launches and may be captured into a CUDA graph,
+ * provided the same call ran once on that stream before the capture began (the call
+ * then finds its workspace in place; one that would have to allocate during capture
+ * returns CPUOPS_B200_STATUS_INVALID_ARGUMENTS instead).  A workspace used under capture
+ * is never freed, so graphs stay valid when later calls on the stream need more room. */
 CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* desc);
 
 /* No counterpart in the reference.  u8 x s8 -> s32 GEMM through the two-stage
@@ -165,9 +178,10 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* desc);
  *   - Same descriptor and epilogue as cpuops_b200_gemm, kind I8 only, k > 0.
  *   - All pointers must be device memory; A and B must be 16-byte aligned with
  *     leading dimensions that are multiples of 16 (nothing can be staged or repacked).
- *   - split_k_slices: 0 picks min(8, k/128); the slices * m * n * 4 bytes of partial
- *     sums must fit the array, otherwise CPUOPS_B200_STATUS_INVALID_ARGUMENTS with a
- *     message naming the size and the limit.
+ *   - split_k_slices: 0 picks as many slices as fit the array, at most
+ *     min(8, ceil(k/128)); a forced count whose slices * m * n * 4 bytes of partial sums
+ *     do not fit (or m * n * 4 alone) is rejected with
+ *     CPUOPS_B200_STATUS_INVALID_ARGUMENTS and a message naming the size and the limit.
  *   - stream == NULL means the legacy default stream (no stream is created).
  *     Synchronous.  FLAG_ASYNC is ignored.
  *   - The first call on a device looks up the array's device address and sets kernel
@@ -175,8 +189,8 @@ CPUOPS_B200_API int cpuops_b200_gemm(const cpuops_b200_gemm_desc* desc);
  *   - All calls share the one array: it keeps the previous call's contents (the
  *     library clears the one word that must start at zero), and two calls whose
  *     kernels overlapped on the GPU would race on it.  The call is synchronous and
- *     serialised inside the library, so this only matters to a caller that loads
- *     two copies of the library into one process.
+ *     serialised per device inside the library, so this only matters to a caller that
+ *     loads two copies of the library into one process.
  * Results are bit-identical to cpuops_b200_gemm on the same descriptor. */
 #define CPUOPS_B200_NOALLOC_SCRATCH_BYTES (8u << 20)
 CPUOPS_B200_API int cpuops_b200_gemm_i8_noalloc(const cpuops_b200_gemm_desc* desc);
@@ -208,6 +222,20 @@ CPUOPS_B200_API int cpuops_b200_shard_rows(int32_t m, int32_t world, int32_t ran
 /* Status of work enqueued with FLAG_ASYNC on `stream` (synchronises it). */
 CPUOPS_B200_API int cpuops_b200_stream_status(void* stream);
 
+/* Budget of every bounded device-side wait (mbarrier waits of the GEMM kernels' roles), in
+ * microseconds; 0 restores the default of one second.  A wait that runs out makes the
+ * kernel record a code, unwind and return; the call (or cpuops_b200_stream_status for
+ * asynchronous calls) then reports CPUOPS_B200_STATUS_DEVICE_TIMEOUT.  Applies to calls
+ * issued after it returns. */
+CPUOPS_B200_API int cpuops_b200_set_wait_budget_us(uint32_t microseconds);
+
+/* Self-test of that path (no counterpart in the reference): launches one warp that waits,
+ * with a budget of `budget_us` (1..100000) microseconds, on a barrier nothing arrives on.
+ * Returns CPUOPS_B200_STATUS_DEVICE_TIMEOUT when the mechanism works -- the wait gave up,
+ * the device error word was set, read and cleared -- and the device stays usable.
+ * Synchronous; `stream` NULL = the library's own stream. */
+CPUOPS_B200_API int cpuops_b200_selftest_wait_timeout(uint32_t budget_us, void* stream);
+
 /* Measurement aid with no counterpart in the reference: while enabled, CUDA
  * events are recorded on the launching stream around every tensor-core GEMM
  * kernel (not the helper kernels).  collect() waits for them, returns the
@@ -226,7 +254,7 @@ CPUOPS_B200_API int cpuops_b200_profile_collect(double* total_ms, int32_t* launc
 CPUOPS_B200_API int cpuops_b200_prepare_b(const cpuops_b200_gemm_desc* d, void** handle);
 CPUOPS_B200_API int cpuops_b200_release_b(void* handle);
 
-/* What the last cpuops_b200_gemm call of this process that reached the tensor-core kernel
+/* What the calling thread's last cpuops_b200_gemm call that reached a tensor-core kernel
  * launched (diagnostics for tests and benchmarks): */
 typedef struct cpuops_b200_plan {
   int32_t swapped;   /* 1: the caller's B went on the MMA M side (small m)          */
@@ -239,6 +267,8 @@ typedef struct cpuops_b200_plan {
   int32_t prepared_b; /* 1: B's scale atoms came from cpuops_b200_prepare_b        */
   int32_t epilogue_warps; /* 4, or 8 (single-wave launches and short k loops)      */
   int32_t narrow_last;    /* 1: a ragged last tile column ran at its own width     */
+  int32_t decode;         /* 1: the small-m MX kernel ran (one launch, raw scales);
+                             `slices` is then the most pieces a weight tile was cut into */
 } cpuops_b200_plan;
 CPUOPS_B200_API int cpuops_b200_last_plan(cpuops_b200_plan* out);
 

@@ -45,12 +45,29 @@ def build_oracle(force: bool = False) -> Path:
     return ORACLE_SO
 
 
-def build_ref(reference: str = "/root/reference") -> bool:
-    """Compile the reference shim when the reference checkout is present."""
-    if not Path(reference, "include", "cpu_ops").is_dir():
+def reference_checkout() -> str:
+    """Path of the reference checkout: the environment variable CPU_OPS_REFERENCE, else a
+    directory named `reference` beside this repository (empty string when neither exists)."""
+    import os
+    for cand in (os.environ.get("CPU_OPS_REFERENCE", ""), str(HERE.parent.parent / "reference")):
+        if cand and Path(cand, "include", "cpu_ops").is_dir():
+            return cand
+    return ""
+
+
+def build_ref(reference: str = "") -> bool:
+    """Compile the reference shim and the reference's own test programs (against this
+    repository's headers and library) when the reference checkout is present."""
+    reference = reference or reference_checkout()
+    if not reference:
         return False
     subprocess.run(["make", "-C", str(HERE), "ref", f"REFERENCE={reference}"], check=True,
                    capture_output=True)
+    res = subprocess.run(["make", "-C", str(HERE), "upstream_tests", f"REFERENCE={reference}"],
+                         capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("the reference's test programs no longer compile against include/:\n" +
+                           res.stdout[-3000:] + res.stderr[-3000:])
     return True
 
 

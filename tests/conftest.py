@@ -37,6 +37,16 @@ def lib():
 
 
 @pytest.fixture(scope="session")
+def lib_instrument():
+    """The library built with -DCPUOPS_B200_INSTRUMENT: it alone exports the launch-policy
+    probes (work order, tile-width choice).  Loaded beside the product library, never
+    instead of it."""
+    import ctypes
+    from cpu_ops_b200 import build
+    return ctypes.CDLL(str(build.build(instrument=True)))
+
+
+@pytest.fixture(scope="session")
 def gpu(lib):
     """Fails (does not skip) when a gpu-marked test runs without a usable device:
     a silent fallback must never look like a pass."""

@@ -15,6 +15,13 @@ from cpu_ops_b200 import _capi, sharding
 ROOT = Path(__file__).resolve().parent.parent
 
 
+def test_product_library_has_no_probe_exports(lib):
+    """The launch-policy probes and cycle counters exist only in the instrumented build."""
+    for name in ("cpuops_b200_debug_slot_to_tile", "cpuops_b200_debug_pick_tile_width",
+                 "cpuops_b200_debug_clock"):
+        assert not hasattr(lib, name), name
+
+
 def test_library_exports_every_declared_symbol(lib):
     header = (ROOT / "include" / "cpu_ops_b200.h").read_text()
     declared = set(re.findall(r"CPUOPS_B200_API\s+[\w\s\*]+?\b(cpuops_b200_\w+)\s*\(", header))
@@ -151,12 +158,12 @@ def test_last_plan_is_readable_before_any_call(lib):
 
 
 @pytest.mark.parametrize("workers", [1, 3, 74, 148])
-def test_narrow_column_work_order_is_a_permutation_and_balances(lib, workers):
+def test_narrow_column_work_order_is_a_permutation_and_balances(lib_instrument, workers):
     """A launch whose last tile column is narrower deals those cheaper tiles to the work
     slots (slot v runs on worker v % workers in round v // workers) so that no worker ends
     a whole wide tile late.  The map must hit every tile exactly once, keep the wide tiles
     in ascending order, and never load a worker more than the plain order would."""
-    f = lib.cpuops_b200_debug_slot_to_tile
+    f = lib_instrument.cpuops_b200_debug_slot_to_tile
     f.argtypes = [C.c_int32] * 4 + [C.POINTER(C.c_int32)] * 2
     f.restype = C.c_int
 
@@ -188,11 +195,11 @@ def test_narrow_column_work_order_is_a_permutation_and_balances(lib, workers):
     assert f(5, 2, 3, workers, C.byref(a), C.byref(b)) == 1      # slot out of range
 
 
-def test_tile_width_choice_for_the_configured_workloads(lib):
+def test_tile_width_choice_for_the_configured_workloads(lib_instrument):
     """The launcher's cost model (148 SMs): 256-wide tiles for int8, 224-wide for MX (two
     accumulators plus the scale slots must fit in tensor memory), also for 4096^3 where a
     64-wide last column evens the rounds out; an n-contiguous B only allows 128 or 256."""
-    f = lib.cpuops_b200_debug_pick_tile_width
+    f = lib_instrument.cpuops_b200_debug_pick_tile_width
     f.argtypes = [C.c_int32] * 7
     f.restype = C.c_int
     sms = 148

@@ -15,6 +15,8 @@ import pytest
 
 import cpu_ops_b200 as c
 from cpu_ops_b200 import _capi, workloads as W
+from oracle.loader import OP_BIAS_ADD, OP_CLAMP, OP_RELU
+from tests.gpu_helpers import run_int8_oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -53,13 +55,17 @@ def _run_both(P, dev, alpha, beta, chain_host, split):
     return outs
 
 
-def test_noalloc_matches_regular_entry_point_twice_in_a_row(gpu):
+def test_noalloc_matches_regular_entry_point_twice_in_a_row(gpu, oracle):
     # first call: all row-major, fused chain, 4 slices
     P1, dev1 = _device_problem(384, 512, 2048, seed=101)
     bias = W.rng_for(101, 9).integers(-(1 << 15), (1 << 15) + 1, size=P1.n, dtype=np.int32)
     reg, noa = _run_both(P1, dev1, 1, 1, [("bias", bias, 0, 0), ("relu", None, 0, 0),
                                            ("clamp", None, 0, 1 << 20)], split=4)
     assert np.array_equal(reg, noa)
+    # ... and both are the CPU oracle's bits, so this file stands on its own
+    want = run_int8_oracle(oracle, P1, 1, 1, ops=[(OP_BIAS_ADD, bias, 0, 0), (OP_RELU, None, 0, 0),
+                                                  (OP_CLAMP, None, 0, 1 << 20)])
+    assert np.array_equal(noa, want)
     # second call right after it: another shape and layout, more slices, so stale partial
     # sums from the first call sit in the shared scratch array and must not leak in
     P2, dev2 = _device_problem(256, 320, 4096, seed=102, lay=0b001)  # A row-, B/C column-major
@@ -68,6 +74,15 @@ def test_noalloc_matches_regular_entry_point_twice_in_a_row(gpu):
     # and the first problem again, automatic slice count
     reg, noa = _run_both(P1, dev1, 1, 0, [], split=0)
     assert np.array_equal(reg, noa)
+
+
+def test_noalloc_automatic_slice_count_fits_the_array(gpu, oracle):
+    """split_k_slices = 0 on a 1024 x 1024 result (4 MiB per slab): eight slices would not
+    fit the 8 MiB array, two do; the automatic mode must pick what fits instead of failing."""
+    P, dev = _device_problem(1024, 1024, 1024, seed=104)
+    reg, noa = _run_both(P, dev, 1, 1, [], split=0)
+    assert np.array_equal(reg, noa)
+    assert np.array_equal(noa, run_int8_oracle(oracle, P, 1, 1))
 
 
 def test_noalloc_rejects_what_it_cannot_hold(gpu):
