@@ -16,6 +16,17 @@ through the synchronous C-ABI call with pinned HOST buffers, host<->device
 copies included; `roofline` is the tensor-core kernel alone, timed live with
 CUDA events on its stream; `cpu_baseline` is the reference's own CPU operator
 (oracle/_ref, built from the unmodified reference headers) on the host cores.
+
+The same line carries, beside the headline:
+  * `suite` (N = 1): one record per configured workload (int8 / mxfp8 / mxfp4 GEMMs at the
+    configured and the 8192^3 / 16384^3 shapes, the decode shapes), each with its call time
+    back to back over rotating operand sets, its kernel time, its launch plan and a
+    roofline against the measured and the nominal peak -- the table the reference's
+    benchmark prints in one run (examples/01_benchmark.cc:204-343);
+  * `sharded` (N > 1): the 16384^3 MX problems cut into output row blocks over the N
+    ranks (B replicated), timed without and with the all-gather of D, each rank's block
+    checked against the CPU oracle at sampled positions and, bit for bit, against
+    rank 0's own single-GPU computation of the same rows.
 """
 from __future__ import annotations
 
@@ -33,6 +44,8 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# nominal per-GPU figures of a B200: dense int8 / fp8, dense fp4 (TOP/s), HBM3e (GB/s)
+NOMINAL_PEAKS = {2.0: 4500.0, 4.0: 9000.0, "hbm_gbs": 8000.0}
 
 
 def load_peaks():
@@ -120,6 +133,51 @@ class Workload:
                          scale_hi=self.scale_hi, seed=seed)
         return dict(A=P.A, SA=P.SA, B=P.B, SB=P.SB, C=P.C, D=np.zeros_like(P.C))
 
+    def device_operands(self, dev, seed, rows=None):
+        """The same operands generated on the device (torch's counter-based generator: the
+        same seed gives the same bytes on every B200), for workloads whose host generation
+        would dominate the run.  MX elements avoid NaN / Inf codes; C is only generated
+        when beta != 0 (otherwise the never-read C argument aliases D)."""
+        import torch
+        from cpu_ops_b200 import _capi
+        rows = self.m if rows is None else rows
+        n, k = self.n, self.k
+        g = torch.Generator(device=dev)
+        g.manual_seed(int(seed))
+
+        def raw(count):
+            return torch.randint(0, 256, (count,), dtype=torch.uint8, device=dev, generator=g)
+
+        if self.kind == "int8":
+            out = dict(A=raw(rows * k), B=raw(k * n).view(torch.int8),
+                       D=torch.empty(rows * n, dtype=torch.int32, device=dev))
+            out["C"] = (torch.randint(-1000, 1001, (rows * n,), dtype=torch.int32, device=dev, generator=g)
+                        if self.beta != 0 else out["D"])
+            if self.chain:
+                out["bias"] = torch.randint(-(1 << 15), (1 << 15) + 1, (n,), dtype=torch.int32, device=dev,
+                                            generator=g)
+            return out
+        per = 2 if self.fmt == _capi.FMT_E2M1 else 1
+        kg = (k + 31) // 32
+
+        def elements(r):
+            x = raw(r * k // per)
+            if self.fmt == _capi.FMT_E4M3:      # 0x7F / 0xFF are NaN
+                x = torch.where((x & 0x7F) == 0x7F, x & 0xFE, x)
+            elif self.fmt == _capi.FMT_E5M2:    # exponent 11111 is Inf / NaN
+                x = torch.where((x & 0x7C) == 0x7C, x & 0xFB, x)
+            return x
+
+        def scales(r):
+            return torch.randint(self.scale_lo, self.scale_hi + 1, (r * kg,), dtype=torch.uint8, device=dev,
+                                 generator=g)
+
+        out = dict(A=elements(rows), SA=scales(rows), B=elements(n), SB=scales(n),
+                   D=torch.empty(rows * n, dtype=torch.float32, device=dev))
+        out["C"] = (torch.randn(rows * n, dtype=torch.float32, device=dev, generator=g)
+                    if self.beta != 0 else out["D"])
+        return out
+
     def operator(self, **kw):
         import cpu_ops_b200 as c
         if self.kind == "int8":
@@ -173,6 +231,31 @@ class Workload:
         """Dense tensor peak relative to bf16: int8/fp8 x2, fp4 x4."""
         from cpu_ops_b200 import _capi
         return 4.0 if (self.kind == "mx" and self.fmt == _capi.FMT_E2M1) else 2.0
+
+    def roofline(self, seconds, peaks, peak_kind, rows=None):
+        """Roofline of one launch that took `seconds`: the bound follows from the arithmetic
+        intensity (ops per compulsory byte) against the machine balance of the measured
+        peaks; the fraction is given against the measured and against the nominal peak."""
+        ops, byts = self.ops(rows), self.min_bytes(rows)
+        tensor_peak = self.peak_factor * float(peaks["bf16_tflops"])
+        hbm_peak = float(peaks["hbm_gbs"])
+        balance = tensor_peak * 1e12 / (hbm_peak * 1e9)
+        bound = "hbm" if (self.bound == "hbm" or ops / byts < balance) else "tensor"
+        if bound == "hbm":
+            achieved = byts / seconds / 1e9 if seconds else None
+            peak, nominal, unit = hbm_peak, NOMINAL_PEAKS["hbm_gbs"], "GB/s"
+            basis = f"hbm_gbs ({peak_kind}); nominal 8000 GB/s"
+        else:
+            achieved = ops / seconds / 1e12 if seconds else None
+            peak, nominal, unit = tensor_peak, NOMINAL_PEAKS[self.peak_factor], "TFLOP/s"
+            basis = (f"{self.peak_factor:g} x bf16_tflops burst ({peak_kind}): dense "
+                     f"{'fp4' if self.peak_factor == 4 else 'int8/fp8'} is nominally {self.peak_factor:g}x "
+                     f"bf16 and no 8/4-bit peak was measured on this pool; nominal {nominal:g} TOP/s")
+        return {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
+                "frac": (achieved / peak) if achieved else None,
+                "peak_nominal": nominal, "frac_nominal": (achieved / nominal) if achieved else None,
+                "intensity_ops_per_byte": ops / byts, "balance_ops_per_byte": balance,
+                "algorithmic_per_launch": byts if bound == "hbm" else ops, "peak_basis": basis}
 
 
 # ---------------------------------------------------------------------------------
@@ -369,6 +452,317 @@ def run_table(args):
     return 0
 
 
+def plan_dict(plan, graph=False):
+    return {"tile": f"{256 if plan.pair else 128}x{plan.tile_n}", "cta_pair": bool(plan.pair),
+            "operands_swapped": bool(plan.swapped), "k_slices": plan.slices, "smem_stages": plan.stages,
+            "ctas": plan.grid, "prepared_b": bool(plan.prepared_b), "small_m_kernel": bool(plan.decode),
+            "cuda_graph": bool(graph)}
+
+
+def _event_ms(fn, count):
+    import torch
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(count):
+        fn(i)
+    e1.record()
+    e1.synchronize()
+    return e0.elapsed_time(e1) / count
+
+
+def measure_workload(wl, dev, lib, peaks, peak_kind, budget_s=0.05, with_graph=False):
+    """One suite record: device-resident operands generated on the device, rotating over
+    enough distinct sets that one trip touches more than twice the L2; the call time back to
+    back (best of three passes), the dominant kernel's own time (CUDA events around it), and
+    for the decode shapes the same calls replayed from a CUDA graph."""
+    import ctypes as C
+    import torch
+    import cpu_ops_b200 as c
+    from cpu_ops_b200 import _capi
+    l2_bytes = torch.cuda.get_device_properties(dev).L2_cache_size
+    first = wl.device_operands(dev, seed=17)
+    set_bytes = sum(v.numel() * v.element_size() for k_, v in first.items() if k_ != "C" or v is not first["D"])
+    n_sets = max(2, -(-2 * l2_bytes // set_bytes) + 1)
+    sets = [first] + [wl.device_operands(dev, seed=17 + i) for i in range(1, n_sets)]
+    stream = torch.cuda.current_stream().cuda_stream
+    op = wl.operator(stream=stream, asynchronous=True, memory_space=_capi.MEM_DEVICE)
+    descs = [op.describe(wl.arguments(op, b)) for b in sets]
+
+    def call(i):
+        st = op.run(descs[i % n_sets])
+        if st != c.Status.kSuccess:
+            raise RuntimeError(f"{wl.name}: GEMM failed: {st!r}: {_capi.last_error()}")
+
+    launches0 = c.launch_count()
+    for i in range(max(3, n_sets)):
+        call(i)
+    torch.cuda.synchronize()
+    launches_per_call = (c.launch_count() - launches0) / max(3, n_sets)
+    if c.stream_status(stream) != c.Status.kSuccess:
+        raise RuntimeError(f"{wl.name}: device-side error: {_capi.last_error()}")
+    plan = _capi.last_plan()
+    est_ms = _event_ms(call, 3)
+    steps = int(min(400, max(10, budget_s * 1e3 / max(est_ms, 1e-3))))
+    passes = [_event_ms(call, steps) for _ in range(3)]
+    t0 = time.perf_counter()
+    for i in range(steps):
+        call(i)
+    host_us = (time.perf_counter() - t0) / steps * 1e6   # issue cost on the host (the GPU lags behind)
+    torch.cuda.synchronize()
+    lib.cpuops_b200_profile(1)
+    for i in range(min(steps, 50)):
+        call(i)
+    torch.cuda.synchronize()
+    lib.cpuops_b200_profile(0)
+    kms, kn = C.c_double(0), C.c_int32(0)
+    lib.cpuops_b200_profile_collect(C.byref(kms), C.byref(kn))
+    kernel_ms = kms.value / kn.value if kn.value else None
+    best_ms = min(passes)
+    rate, unit = rate_of(wl, wl.m, best_ms / 1e3)
+    rec = {"workload": wl.name, "m": wl.m, "n": wl.n, "k": wl.k, "alpha": wl.alpha, "beta": wl.beta,
+           "dtype": wl.dtype, "operand_sets": n_sets, "steps": steps,
+           "ms_per_call": best_ms, "ms_per_call_passes": passes, "host_issue_us_per_call": host_us,
+           "launches_per_call": launches_per_call, "kernel_ms": kernel_ms,
+           "value": rate, "unit": unit, "kernel_plan": plan_dict(plan),
+           "roofline_call": wl.roofline(best_ms / 1e3, peaks, peak_kind),
+           "roofline_kernel": wl.roofline(kernel_ms / 1e3, peaks, peak_kind) if kernel_ms else None}
+    if with_graph:
+        # The same calls replayed from a CUDA graph: what a launch-bound decode loop would do.
+        # The capture stream runs the calls once before the capture begins (workspace, counters).
+        side = torch.cuda.Stream(device=dev)
+        op_g = wl.operator(stream=side.cuda_stream, asynchronous=True, memory_space=_capi.MEM_DEVICE)
+        descs_g = [op_g.describe(wl.arguments(op_g, b)) for b in sets]
+        with torch.cuda.stream(side):
+            for dsc in descs_g:
+                op_g.run(dsc)
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side, capture_error_mode="relaxed"):
+                for dsc in descs_g:
+                    st = op_g.run(dsc)
+                    if st != c.Status.kSuccess:
+                        raise RuntimeError(f"{wl.name}: capture failed: {st!r}: {_capi.last_error()}")
+            for _ in range(3):
+                graph.replay()
+            side.synchronize()
+            trips = max(3, steps // n_sets)
+            best_g = min(_event_ms(lambda i: graph.replay(), trips) for _ in range(3)) / n_sets
+        rec["graph_ms_per_call"] = best_g
+        rec["roofline_graph"] = wl.roofline(best_g / 1e3, peaks, peak_kind)
+        del graph
+    del sets, descs
+    torch.cuda.empty_cache()
+    return rec
+
+
+def run_suite(dev, lib, peaks, peak_kind):
+    out = []
+    for name in TABLE_WORKLOADS:
+        wl = Workload(name)
+        out.append(measure_workload(wl, dev, lib, peaks, peak_kind, with_graph=wl.bound == "hbm"))
+    return out
+
+
+# ---------------------------------------------------------------------------------
+# N > 1: the 16384^3 MX problems, output row blocks over the ranks
+# ---------------------------------------------------------------------------------
+def _decode_f64(fmt, codes):
+    """Exact decode of MX element codes to float64 (numpy): e5m2 is the upper byte of an
+    IEEE half, e4m3 / e2m1 by table."""
+    from cpu_ops_b200 import _capi
+    codes = np.asarray(codes, dtype=np.uint8)
+    if fmt == _capi.FMT_E5M2:
+        return (codes.astype(np.uint16) << 8).view(np.float16).astype(np.float64)
+    if fmt == _capi.FMT_E2M1:
+        mag = np.array([0, .5, 1, 1.5, 2, 3, 4, 6], np.float64)
+        return np.where(codes & 8, -1.0, 1.0) * mag[codes & 7]
+    e, mnt = (codes >> 3) & 0xF, (codes & 7).astype(np.float64)
+    val = np.where(e == 0, mnt * 2.0 ** -9, (8 + mnt) * 2.0 ** (e.astype(np.float64) - 10))
+    return np.where(codes & 0x80, -val, val)
+
+
+def sampled_f64_reference(wl, A_rows, SA_rows, B_rows, SB_rows):
+    """D[i, j] in double for the given operand rows (host arrays: elements as stored, scales
+    one byte per 32 k): decode exactly, apply the E8M0 scales, accumulate in float64 -- the
+    arithmetic of the reference's own test (test/test_gemm_mx.cc:181-197), written here in
+    numpy so that the bench needs nothing from the test-side oracle."""
+    from cpu_ops_b200 import _capi
+    k = wl.k
+
+    def expand(data, scl):
+        r = data.shape[0]
+        if wl.fmt == _capi.FMT_E2M1:
+            lo, hi = data & 0xF, data >> 4
+            codes = np.stack([lo, hi], axis=-1).reshape(r, k)   # even k in the low nibble
+        else:
+            codes = data.reshape(r, k)
+        sc = np.exp2(scl.reshape(r, k // 32).astype(np.float64) - 127.0)
+        return _decode_f64(wl.fmt, codes) * np.repeat(sc, 32, axis=1)
+
+    return wl.alpha * (expand(A_rows, SA_rows) @ expand(B_rows, SB_rows).T)
+
+
+def run_sharded(args, rank, world, dev, lib, peaks, peak_kind):
+    """Each 16384^3 MX problem cut into output row blocks (cpuops_b200_shard_rows); every rank
+    holds its rows of A and all of B.  Timed: the GEMM steps alone, and the same steps each
+    followed by an all-gather of the D blocks into a replicated D (NCCL, on a second stream,
+    two D buffers, so the gather of step i runs under the GEMM of step i + 1).  Checked,
+    outside the timed region: sampled elements of every rank's block against a float64
+    reference on the CPU, and the first rows of every block, bit for bit, against rank 0's
+    single-GPU computation of the same rows."""
+    import torch
+    import torch.distributed as dist
+    import cpu_ops_b200 as c
+    from cpu_ops_b200 import _capi, sharding
+    out = {}
+    steps = max(5, min(args.steps, 20))
+    for name in ("mx_e5m2_16384", "mx_e2m1_16384"):
+        wl = Workload(name)
+        M, n, k = wl.m, wl.n, wl.k
+        per = 2 if wl.fmt == _capi.FMT_E2M1 else 1
+        kg = k // 32
+        sh = sharding.shard_rows(M, world, rank)
+        r0, rn = sh.row_begin, sh.row_count
+        assert rn * world == M, "the bench assumes equal row blocks"
+        full = wl.device_operands(dev, seed=0xC5C5 + wl.fmt)   # the whole problem, identical on every rank
+        a_rows = lambda lo, cnt: full["A"][lo * k // per:(lo + cnt) * k // per]
+        sa_rows = lambda lo, cnt: full["SA"][lo * kg:(lo + cnt) * kg]
+        d_blk = [torch.empty(rn * n, dtype=torch.float32, device=dev) for _ in range(2)]
+        stream = torch.cuda.current_stream().cuda_stream
+        op = wl.operator(stream=stream, asynchronous=True, memory_space=_capi.MEM_DEVICE)
+
+        def describe(lo, cnt, dbuf):
+            bufs = dict(A=a_rows(lo, cnt), SA=sa_rows(lo, cnt), B=full["B"], SB=full["SB"], C=dbuf, D=dbuf)
+            return op.describe(wl.arguments(op, bufs, rows=cnt))
+
+        descs = [describe(r0, rn, d_blk[j]) for j in range(2)]
+
+        def gemm(i):
+            st = op.run(descs[i % 2])
+            if st != c.Status.kSuccess:
+                raise RuntimeError(f"sharded {name}: GEMM failed: {st!r}: {_capi.last_error()}")
+
+        def timed(fn, count):
+            dist.barrier()
+            torch.cuda.synchronize()
+            ms = _event_ms(fn, count)
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+
+        for i in range(3):
+            gemm(i)
+        gemm_ms = timed(gemm, steps)
+        plan = _capi.last_plan()
+
+        # with the all-gather of D: gather of step i on a second stream under GEMM i + 1
+        d_full = [torch.empty(M * n, dtype=torch.float32, device=dev) for _ in range(2)]
+        side = torch.cuda.Stream(device=dev)
+        ready = [torch.cuda.Event() for _ in range(2)]
+        done = [None, None]
+
+        def gemm_then_gather(i):
+            j = i % 2
+            if done[j] is not None:
+                torch.cuda.current_stream().wait_event(done[j])   # the gather that read d_blk[j] is over
+            gemm(i)
+            ready[j].record(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                side.wait_event(ready[j])
+                dist.all_gather_into_tensor(d_full[j], d_blk[j])
+                if done[j] is None:
+                    done[j] = torch.cuda.Event()
+                done[j].record(side)
+
+        def gathered(count):
+            def body(i):
+                gemm_then_gather(i)
+                if i == count - 1:
+                    torch.cuda.current_stream().wait_stream(side)
+            return body
+
+        for i in range(3):
+            gemm_then_gather(i)
+        torch.cuda.current_stream().wait_stream(side)
+        with_gather_ms = timed(gathered(steps), steps)
+        gather_ms = timed(lambda i: dist.all_gather_into_tensor(d_full[0], d_blk[0]), steps)
+
+        # ---- checks (not timed) ----
+        torch.cuda.synchronize()
+        gemm(0)
+        torch.cuda.synchronize()
+        D = d_blk[0].view(rn, n)
+        # the replicated D really is the blocks in rank order
+        dist.all_gather_into_tensor(d_full[0], d_blk[0])
+        torch.cuda.synchronize()
+        gather_ok = bool(torch.equal(d_full[0].view(M, n)[r0:r0 + rn].view(torch.int32), D.view(torch.int32)))
+        # (1) sampled positions against float64 on the CPU
+        gsel = torch.Generator(device="cpu")
+        gsel.manual_seed(1234 + rank)
+        ri = torch.randperm(rn, generator=gsel)[:16].sort().values
+        cj = torch.randperm(n, generator=gsel)[:64].sort().values
+        A_h = full["A"].view(M, k // per)[r0 + ri.to(dev)].cpu().numpy()
+        SA_h = full["SA"].view(M, kg)[r0 + ri.to(dev)].cpu().numpy()
+        B_h = full["B"].view(n, k // per)[cj.to(dev)].cpu().numpy()
+        SB_h = full["SB"].view(n, kg)[cj.to(dev)].cpu().numpy()
+        want = sampled_f64_reference(wl, A_h, SA_h, B_h, SB_h)
+        got = D[ri.to(dev)][:, cj.to(dev)].cpu().numpy().astype(np.float64)
+        err = float(np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-300))
+        # (2) the first rows of every block, bit for bit, against rank 0 computing them alone
+        sub = min(1024, rn)
+        mine = D[:sub].contiguous().view(-1)
+        everyone = torch.empty(world * sub * n, dtype=torch.float32, device=dev)
+        dist.all_gather_into_tensor(everyone, mine)
+        bits_ok = True
+        if rank == 0:
+            alone = torch.empty(sub * n, dtype=torch.float32, device=dev)
+            for j in range(world):
+                rj = sharding.shard_rows(M, world, j).row_begin
+                st = op.run(describe(rj, sub, alone))
+                torch.cuda.synchronize()
+                bits_ok = bits_ok and st == c.Status.kSuccess and bool(
+                    torch.equal(alone.view(torch.int32), everyone[j * sub * n:(j + 1) * sub * n].view(torch.int32)))
+        flags = torch.tensor([1.0 if (err <= 1e-5 and bits_ok and gather_ok) else 0.0, -err], device=dev,
+                             dtype=torch.float64)
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+        # the whole problem on one GPU, for the strong-scaling ratio (rank 0 only; others wait)
+        single_ms = None
+        if rank == 0:
+            d_whole = d_full[1]
+            whole = describe(0, M, d_whole)
+            for _ in range(2):
+                op.run(whole)
+            torch.cuda.synchronize()
+            single_ms = _event_ms(lambda i: op.run(whole), 5)
+        dist.barrier()
+        if c.stream_status(stream) != c.Status.kSuccess:
+            raise RuntimeError(f"sharded {name}: device-side error: {_capi.last_error()}")
+        if rank == 0:
+            ops = wl.ops()
+            blk_bytes = rn * n * 4
+            out[name] = {
+                "m": M, "n": n, "k": k, "rows_per_rank": rn, "steps": steps, "kernel_plan": plan_dict(plan),
+                "ms_per_step": gemm_ms, "tflops_aggregate": ops / (gemm_ms / 1e3) / 1e12,
+                "tflops_per_gpu": ops / world / (gemm_ms / 1e3) / 1e12,
+                "single_gpu_ms_per_step": single_ms,
+                "strong_scaling_efficiency": single_ms / (world * gemm_ms),
+                "with_gather": {"ms_per_step": with_gather_ms,
+                                "tflops_aggregate": ops / (with_gather_ms / 1e3) / 1e12,
+                                "strong_scaling_efficiency": single_ms / (world * with_gather_ms)},
+                "gather_alone": {"ms": gather_ms, "bytes_received_per_rank": (world - 1) * blk_bytes,
+                                 "nvlink_gbs_received_per_rank": (world - 1) * blk_bytes / (gather_ms / 1e3) / 1e9},
+                "parity_ok": bool(flags[0].item() == 1.0), "worst_sampled_normwise_error": float(-flags[1].item()),
+                "parity_checks": "per rank: 16 x 64 sampled elements vs a float64 CPU reference (<= 1e-5 "
+                                 "normwise); first 1024 rows of every block bit-identical to rank 0's "
+                                 "single-GPU run of those rows; gathered D equals the blocks in rank order",
+                "l2": "per-rank inputs (A rows + all of B) exceed the L2",
+            }
+        del full, d_blk, d_full
+        torch.cuda.empty_cache()
+    return out
+
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -388,6 +782,10 @@ def main():
     ap.add_argument("--graph", action="store_true",
                     help="replay the calls from a CUDA graph (one trip round the operand ring per "
                          "replay), as a launch-bound decode loop would; steps are rounded to whole trips")
+    ap.add_argument("--no-suite", action="store_true",
+                    help="N = 1: skip the per-workload `suite` records (headline only)")
+    ap.add_argument("--no-sharded", action="store_true",
+                    help="N > 1: skip the row-sharded 16384^3 `sharded` leg (headline only)")
     ap.add_argument("--prepared-b", action="store_true",
                     help="MX workloads: register each B operand once (cpuops_b200_prepare_b), as a "
                          "decode loop with fixed weights would")
@@ -467,22 +865,24 @@ def main():
     step = direct_step
     graph, launches_per_trip = None, 0
     if args.graph:
-        # Capture one call per operand set on torch's capture stream; the library's calls
-        # are plain kernel launches once its workspace for that stream exists (the first
-        # capture pass below creates it; relaxed mode permits that allocation).
+        # Capture one call per operand set.  The capture stream first runs every call once
+        # outside capture: the library's calls are plain kernel launches once its workspace
+        # for that stream exists, and it refuses to allocate while a capture is under way.
         args.steps = max(n_sets, args.steps // n_sets * n_sets)
         args.warmup = max(n_sets, args.warmup // n_sets * n_sets)
-        for i in range(n_sets):  # the prepared-B copies and tensor maps exist before capture
-            direct_step(i)
-        torch.cuda.synchronize()
+        cap = torch.cuda.Stream(device=dev)
+        op_g = wl.operator(stream=cap.cuda_stream, asynchronous=True, tile_n=args.tile_n,
+                           memory_space=_capi.MEM_DEVICE)
+        descs_g = [op_g.describe(wl.arguments(op_g, b)) for b in sets]
+        with torch.cuda.stream(cap):
+            for dsc in descs_g:
+                op_g.run(dsc)
+            cap.synchronize()
         graph = torch.cuda.CUDAGraph()
         launches_before_capture = c.launch_count()
-        with torch.cuda.graph(graph, capture_error_mode="relaxed"):
-            cap_stream = torch.cuda.current_stream().cuda_stream
-            op_g = wl.operator(stream=cap_stream, asynchronous=True, tile_n=args.tile_n,
-                               memory_space=_capi.MEM_DEVICE)
-            for b in sets:
-                st = op_g.run(op_g.describe(wl.arguments(op_g, b)))
+        with torch.cuda.graph(graph, stream=cap, capture_error_mode="relaxed"):
+            for dsc in descs_g:
+                st = op_g.run(dsc)
                 if st != c.Status.kSuccess:
                     raise RuntimeError(f"GEMM failed during capture: {st!r}: {_capi.last_error()}")
 
@@ -568,40 +968,39 @@ def main():
                "ms_per_step": t_e2e / e2e_steps * 1e3, "steps": e2e_steps}
     sampler.stop()
 
+    # ---- the other workloads (N = 1) / the row-sharded 16384^3 problems (N > 1) ----
+    del sets, descs
+    torch.cuda.empty_cache()
+    suite = sharded = None
+    if world == 1 and not args.no_suite and not args.graph:
+        suite = run_suite(dev, lib, peaks, peak_kind)
+    if world > 1 and not args.no_sharded:
+        sharded = run_sharded(args, rank, world, dev, lib, peaks, peak_kind)
+
     if rank == 0:
         sec_per_step = ms / 1e3 / args.steps
         value, unit = rate_of(wl, wl.m * world, sec_per_step)
         # roofline of the dominant (tensor-core) kernel, per launch
         k_avg_s = (kms.value / 1e3 / kn.value) if kn.value else None
-        if wl.bound == "hbm":
-            peak = float(peaks["hbm_gbs"])
-            achieved = wl.min_bytes() / k_avg_s / 1e9 if k_avg_s else None
-            r_unit, basis = "GB/s", f"hbm_gbs ({peak_kind})"
-        else:
-            peak = wl.peak_factor * float(peaks["bf16_tflops"])
-            achieved = wl.ops() / k_avg_s / 1e12 if k_avg_s else None
-            r_unit = "TFLOP/s"
-            basis = (f"{wl.peak_factor:g} x bf16_tflops burst ({peak_kind}): dense "
-                     f"{'fp4' if wl.peak_factor == 4 else 'int8/fp8'} is nominally "
-                     f"{wl.peak_factor:g}x bf16; no 8/4-bit peak was measured on this pool")
-        traffic = KERNEL_DRAM_TRAFFIC.get(wl.name)
-        roofline = {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": r_unit,
-                    "frac": (achieved / peak) if achieved else None, "traffic": traffic,
-                    "kernel": "gemm_tcgen05_kernel", "kernel_ms": (k_avg_s * 1e3) if k_avg_s else None,
-                    "timed_launches": kn.value, "peak_basis": basis,
-                    "timed_in": "the K steps repeated directly after the timed region, CUDA events "
-                                "around each launch of this kernel on the launching stream",
-                    "algorithmic_per_launch": wl.ops() if wl.bound == "tensor" else wl.min_bytes()}
+        roofline = wl.roofline(k_avg_s, peaks, peak_kind)
+        plan_now = plan_dict(plan, args.graph)
+        cap = KERNEL_DRAM_TRAFFIC.get(wl.name)
+        traffic_ok = cap is not None and cap["tile"] == plan_now["tile"] and cap["k_slices"] == plan_now["k_slices"]
+        roofline.update({
+            "traffic": cap["bytes"] if traffic_ok else None,
+            "traffic_source": (f"ncu capture summarised in {cap['capture']} (dram__bytes_read.sum + "
+                               f"dram__bytes_write.sum per launch, plan {cap['tile']})" if traffic_ok else
+                               "no ncu capture of this kernel plan is on file"),
+            "kernel": "decode_mx_kernel" if plan.decode else "gemm_tcgen05_kernel",
+            "kernel_ms": (k_avg_s * 1e3) if k_avg_s else None, "timed_launches": kn.value,
+            "timed_in": "the K steps repeated directly after the timed region, CUDA events "
+                        "around each launch of this kernel on the launching stream"})
         line = {
             "metric": metric_name(wl), "value": value, "unit": unit, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
             "data": "synthetic",
-            "config": dict(config_of(wl, world), kernel_plan={
-                "tile": f"{256 if plan.pair else 128}x{plan.tile_n}", "cta_pair": bool(plan.pair),
-                "operands_swapped": bool(plan.swapped), "k_slices": plan.slices,
-                "smem_stages": plan.stages, "ctas": plan.grid, "prepared_b": bool(plan.prepared_b),
-                "cuda_graph": bool(args.graph)},
+            "config": dict(config_of(wl, world), kernel_plan=plan_now,
                 gather_d=bool(args.gather and world > 1),
                 seeds=f"operand set s of rank r: 1000*r + s (numpy PCG64 streams per operand, "
                       f"cpu_ops_b200/workloads.py)"),
@@ -610,6 +1009,10 @@ def main():
         }
         if e2e:
             line["e2e"] = e2e
+        if suite is not None:
+            line["suite"] = suite
+        if sharded is not None:
+            line["sharded"] = sharded
         if world == 1 and not args.no_cpu_baseline:
             r = time_reference(wl, steps=3, warmup=1, budget_s=15.0)
             if r is not None:
@@ -628,13 +1031,16 @@ def main():
     return 0
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of gemm_tcgen05_kernel from
-# the ncu captures summarised under profiles/ (None until captured for that workload).
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
+# captures summarised under profiles/, with the launch plan each capture was taken under: the
+# figure is only quoted for a run that launches the same plan.
 KERNEL_DRAM_TRAFFIC = {
-    "mxfp8_e4m3_4096": 123.07e6 + 38.85e6,
-    "int8_8192": 367.55e6 + 235.98e6,
-    "int8_2048": 25.24e6,
-    "mxfp4_decode_m8": 31.32e6,
+    "mxfp8_e4m3_4096": {"bytes": 123.07e6 + 38.85e6, "tile": "256x224", "k_slices": 1,
+                        "capture": "profiles/gemm_tcgen05_kernel_mxfp8_e4m3_4096.md"},
+    "int8_8192": {"bytes": 367.55e6 + 235.98e6, "tile": "256x256", "k_slices": 1,
+                  "capture": "profiles/gemm_tcgen05_kernel_int8_8192.md"},
+    "int8_2048": {"bytes": 25.24e6, "tile": "128x256", "k_slices": 1,
+                  "capture": "profiles/gemm_tcgen05_kernel_int8_2048.md"},
 }
 
 if __name__ == "__main__":
