@@ -470,11 +470,12 @@ def _event_ms(fn, count):
     return e0.elapsed_time(e1) / count
 
 
-def measure_workload(wl, dev, lib, peaks, peak_kind, budget_s=0.05, with_graph=False):
+def measure_workload(wl, dev, lib, peaks, peak_kind, budget_s=0.25, with_graph=False):
     """One suite record: device-resident operands generated on the device, rotating over
     enough distinct sets that one trip touches more than twice the L2; the call time back to
-    back (best of three passes), the dominant kernel's own time (CUDA events around it), and
-    for the decode shapes the same calls replayed from a CUDA graph."""
+    back (mean of three passes; the best pass is reported beside it), the dominant kernel's
+    own time (CUDA events around it), and for the decode shapes the same calls replayed from
+    a CUDA graph."""
     import ctypes as C
     import torch
     import cpu_ops_b200 as c
@@ -502,29 +503,36 @@ def measure_workload(wl, dev, lib, peaks, peak_kind, budget_s=0.05, with_graph=F
         raise RuntimeError(f"{wl.name}: device-side error: {_capi.last_error()}")
     plan = _capi.last_plan()
     est_ms = _event_ms(call, 3)
-    steps = int(min(400, max(10, budget_s * 1e3 / max(est_ms, 1e-3))))
-    passes = [_event_ms(call, steps) for _ in range(3)]
-    t0 = time.perf_counter()
-    for i in range(steps):
-        call(i)
-    host_us = (time.perf_counter() - t0) / steps * 1e6   # issue cost on the host (the GPU lags behind)
-    torch.cuda.synchronize()
+    steps = int(min(2000, max(10, budget_s * 1e3 / max(est_ms, 1e-3))))
+    passes = [_event_ms(call, steps)]
+    # the dominant kernel alone, between the passes (same thermal / power state): CUDA events
+    # around every launch of it, which for a kernel of a few microseconds also bracket the
+    # launch gap the events themselves open (no overlap with its neighbours)
     lib.cpuops_b200_profile(1)
-    for i in range(min(steps, 50)):
+    for i in range(min(steps, 100)):
         call(i)
     torch.cuda.synchronize()
     lib.cpuops_b200_profile(0)
     kms, kn = C.c_double(0), C.c_int32(0)
     lib.cpuops_b200_profile_collect(C.byref(kms), C.byref(kn))
     kernel_ms = kms.value / kn.value if kn.value else None
-    best_ms = min(passes)
-    rate, unit = rate_of(wl, wl.m, best_ms / 1e3)
+    passes += [_event_ms(call, steps) for _ in range(2)]
+    t0 = time.perf_counter()
+    for i in range(steps):
+        call(i)
+    host_us = (time.perf_counter() - t0) / steps * 1e6   # issue cost on the host (the GPU lags behind)
+    torch.cuda.synchronize()
+    mean_ms, best_ms = sum(passes) / len(passes), min(passes)
+    rate, unit = rate_of(wl, wl.m, mean_ms / 1e3)
     rec = {"workload": wl.name, "m": wl.m, "n": wl.n, "k": wl.k, "alpha": wl.alpha, "beta": wl.beta,
-           "dtype": wl.dtype, "operand_sets": n_sets, "steps": steps,
-           "ms_per_call": best_ms, "ms_per_call_passes": passes, "host_issue_us_per_call": host_us,
-           "launches_per_call": launches_per_call, "kernel_ms": kernel_ms,
+           "dtype": wl.dtype, "operand_sets": n_sets, "steps_per_pass": steps,
+           "ms_per_call": mean_ms, "ms_per_call_best_pass": best_ms, "ms_per_call_passes": passes,
+           "host_issue_us_per_call": host_us, "launches_per_call": launches_per_call,
+           "kernel_ms": kernel_ms,
+           "kernel_ms_how": "CUDA events around each launch of the dominant kernel (for kernels of a few "
+                            "microseconds this includes the launch gap that the events open)",
            "value": rate, "unit": unit, "kernel_plan": plan_dict(plan),
-           "roofline_call": wl.roofline(best_ms / 1e3, peaks, peak_kind),
+           "roofline": wl.roofline(mean_ms / 1e3, peaks, peak_kind),
            "roofline_kernel": wl.roofline(kernel_ms / 1e3, peaks, peak_kind) if kernel_ms else None}
     if with_graph:
         # The same calls replayed from a CUDA graph: what a launch-bound decode loop would do.

@@ -30,7 +30,6 @@ OP_RELU, OP_CLAMP, OP_BIAS_ADD, OP_SCALE_PER_ROW, OP_SCALE_PER_COL, OP_GELU, OP_
 MEM_AUTO, MEM_HOST, MEM_DEVICE = 0, 1, 2
 FLAG_ASYNC = 1
 FLAG_PAIR_ON, FLAG_PAIR_OFF = 2, 4
-FLAG_B_IMMUTABLE = 8
 NOALLOC_SCRATCH_BYTES = 8 << 20
 
 # Every symbol include/cpu_ops_b200.h declares.

@@ -149,7 +149,7 @@ int pick_tile_width(int Mk, int Nk, int k_blocks, bool is_mx, int sms, bool beta
 
 struct DecodePlan {
   bool use = false;
-  int BN = 32, tiles = 0, grid = 0, stages = 0, tile_aligned = 0, max_pieces = 1, tmem_cols = 128, w_early = 0;
+  int BN = 32, tiles = 0, grid = 0, stages = 0, tile_aligned = 0, max_pieces = 1, tmem_cols = 128;
   size_t partial_bytes = 0;
   int smem = 0;
 };
@@ -157,27 +157,24 @@ struct DecodePlan {
 // Grid, ranges and buffers of a decode launch: Mk weight rows (128-row tiles), Nk <= 64
 // activation rows, k_blocks 128-byte k-blocks.  Every CTA takes an equal share of the
 // (tile, k-block) units; `never_split` (split_k_slices == 1) keeps whole tiles together.
-DecodePlan plan_decode(const DeviceState& st, int kind, int Mk, int Nk, int k_blocks, bool never_split,
-                       bool w_immutable) {
+DecodePlan plan_decode(const DeviceState& st, int kind, int Mk, int Nk, int k_blocks, bool never_split) {
   DecodePlan dp;
   dp.use = true;
-  dp.w_early = w_immutable ? 1 : 0;
   dp.BN = Nk <= 32 ? 32 : 64;
   dp.tiles = (Mk + kTileM - 1) / kTileM;
   const int ka = kind == kKindMxf4 ? 2 : 1;
   const int per_stage = decode_stage_bytes(Nk) + 2 * ka * 512;
-  // One CTA per SM with the deepest ring the shared memory allows (the stream needs the
-  // bytes in flight).  With immutable weights two smaller CTAs fit an SM instead, so that the
-  // next call's CTAs are resident, their first ring of W already loading, while this call's
-  // are still streaming.
-  int ctas_per_sm = w_immutable ? 2 : 1;
+  // One CTA per SM with the deepest ring the shared memory allows: the stream needs the
+  // bytes in flight (two smaller CTAs per SM measured slower).
+  int ctas_per_sm = 1;
   if (env_switches().decode_ctas_per_sm > 0) ctas_per_sm = env_switches().decode_ctas_per_sm;
   const int64_t units = static_cast<int64_t>(dp.tiles) * k_blocks;
   const int cap = st.sm_count * ctas_per_sm;
   int grid;
   if (never_split || 4 * dp.tiles >= cap) {
     // whole tiles per CTA: no partial sums.  (Measured on 112 tiles: cutting k to feed all
-    // 148 SMs does not shorten the stream, and the reduction through L2 costs 4 us.)
+    // 148 SMs does not shorten the stream, and the reduction through L2 costs 4 us.)  k is
+    // only cut when the tiles are too few to keep even a quarter of the SMs busy.
     grid = std::min(dp.tiles, cap);
     dp.tile_aligned = 1;
   } else {
@@ -789,8 +786,7 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
       return (!on_device || (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0) && (rows <= 1 || ld % 16 == 0);
     };
     if (scales_ok(d->a_scales, sa_dev, d->ld_scales_a, m) && scales_ok(d->b_scales, sb_dev, d->ld_scales_b, n))
-      dp = plan_decode(st, kind, n, m, k_blocks, d->split_k_slices == 1,
-                       (d->flags & CPUOPS_B200_FLAG_B_IMMUTABLE) != 0);
+      dp = plan_decode(st, kind, n, m, k_blocks, d->split_k_slices == 1);
   }
 
   if (depth == 0 && k > 0 && !a_dev && !d_dev && !ch.swap && ch.slices == 1 && m >= 1024)
@@ -1009,7 +1005,6 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     q.ld_sx = d->ld_scales_a;
     q.sw = sb_ptr;
     q.sx = sa_ptr;
-    q.w_early = dp.w_early;
     q.tiles = dp.tiles;
     q.k_blocks = k_blocks;
     q.BN = dp.BN;

@@ -21,21 +21,23 @@
 //     through the epilogue directly, the others are written as partial sums and the warp
 //     that arrives last for a (tile, lane quarter) adds the pieces in ascending k order --
 //     a fixed order, so results do not depend on which CTA finished first.
-//   * Launched with programmatic stream serialization: the CTAs may become resident, set up
-//     their barriers and tensor memory, while the kernel before this one in the stream is
-//     still running; every role then waits (griddepcontrol.wait) before it reads or writes
-//     global memory.  When the caller has declared the weights immutable
-//     (CPUOPS_B200_FLAG_B_IMMUTABLE) the first ring of W tiles and W scales is loaded BEFORE
-//     that wait, and the launcher sizes the CTA so that two fit an SM: in a loop of such
-//     calls the next call's CTAs then sit beside the current one's with their first
-//     stages already in shared memory.  Measured on 14336 x 4096 fp4 weights, per call in
-//     a loop: 14.6 us for the general kernel (two launches), 10.1 us for this kernel, of
-//     which the HBM stream is 5 us, the first bytes' latency 1.3 us, the tail after the
-//     last byte 1.3 us and the gap between a kernel's end and its successor passing the wait
-//     1.3 us.  Asking W into L2 ahead of the wait (prefetch instructions, 256-byte fill
-//     hints, TMA prefetch boxes) was measured too and did not help: issued from a CTA that
-//     is resident a kernel or two early the lines are gone again when they are needed,
-//     and the TMA form costs the TMA unit as much time as the loads.
+//   * Launched with programmatic stream serialization: a CTA may become resident and set up
+//     its barriers and tensor memory while the kernel before this one in the stream is
+//     still finishing; every role then waits (griddepcontrol.wait) before it reads or
+//     writes global memory.
+//
+// Where the time of one call goes (14336 x 4096 fp4 weights, m = 8, calls back to back,
+// time stamps of every role in an instrumented build): 10.1 us per call against 14.6 us for
+// the general kernel with its separate re-layout launch; of these the HBM stream itself is
+// 5.0 us (5.9 TB/s), the latency of the first bytes after the wait 1.3 us, the tail after
+// the last byte 1.3 us and the gap between a kernel's last CTA leaving and its successor
+// passing the wait 1.3 us.  Tried and not kept, each measured on the same loop: cutting k
+// so that all 148 SMs stream (the reduction through L2 costs 4 us, the stream gets no
+// shorter); asking W into L2 ahead of the wait with prefetch instructions, 256-byte fill
+// hints or TMA prefetch boxes (no gain; the TMA form costs the TMA unit as much as the
+// loads); two smaller CTAs per SM so that the next call's CTAs sit beside this call's,
+// with or without loading their first ring of W before the wait (the shallower ring
+// slows the stream by what the overlap saves).
 //
 // Roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer (owns tensor memory), warps
 // 2-5 scale writers (thread = tile row), warps 6-9 epilogue (one TMEM lane quarter each).
@@ -60,7 +62,6 @@ struct DecodeParams {
   int32_t ld_sw, ld_sx;      // leading dimensions of the two scale arrays (bytes)
   const uint8_t* sw;         // W's scales (row-major, 16-byte aligned rows)
   const uint8_t* sx;         // X's scales
-  int32_t w_early;           // 1: W and its scales may be loaded before the stream dependency resolves
   int32_t tiles, k_blocks;   // 128-row tiles of W, 128-byte k-blocks
   int32_t BN;                // 32 or 64
   int32_t stages;
@@ -142,7 +143,7 @@ __device__ __forceinline__ uint32_t pick_word(const uint4& v, int i) {
 }
 
 template <int KIND>
-__global__ void __launch_bounds__(kDecodeThreads, 2)
+__global__ void __launch_bounds__(kDecodeThreads, 1)
     decode_mx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                      const DecodeParams p) {
   static_assert(KIND == kKindMxf8 || KIND == kKindMxf4, "MX kinds only");
@@ -225,38 +226,21 @@ __global__ void __launch_bounds__(kDecodeThreads, 2)
     auto issue_x = [&](int s, int kb) {
       tma_load_2d_g<false>(smem_base + s * stage_bytes + kTileM * 128, &tmX, full_bar(s), kb * 128, 0, el);
     };
-    int first = 0;
-    if (p.w_early) {
-      // the weights cannot change under us: their first ring of tiles need not wait for
-      // the previous kernel in the stream (the barrier is armed with the whole stage's
-      // bytes; the X tile follows after the wait)
-      first = min(stages, n_units);
-      int t2 = tile0, k2 = kb0;
-      for (int i = 0; i < first; ++i) {
-        mbar_expect_tx_p(full_bar(i), tx_bytes, el);
-        issue_w(i, t2, k2);
-        if (++k2 == KB) { k2 = 0; ++t2; }
-      }
-    }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     DECODE_STAMP(p, 2, el);
     int s = 0, tile = tile0, kb = kb0;
     uint32_t ph = 0;
     for (int i = 0; i < n_units; ++i) {
-      if (i < first) {
-        issue_x(s, kb);
-      } else {
-        if (!__all_sync(0xffffffffu, mbar_wait_bounded(empty_bar(s), ph ^ 1u, abort_flag, budget_ns))) {
-          if (el) {
-            atomicCAS(p.error, 0, kErrProducerWait);
-            *abort_flag = 1;
-          }
-          break;
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(empty_bar(s), ph ^ 1u, abort_flag, budget_ns))) {
+        if (el) {
+          atomicCAS(p.error, 0, kErrProducerWait);
+          *abort_flag = 1;
         }
-        mbar_expect_tx_p(full_bar(s), tx_bytes, el);
-        issue_w(s, tile, kb);
-        issue_x(s, kb);
+        break;
       }
+      mbar_expect_tx_p(full_bar(s), tx_bytes, el);
+      issue_w(s, tile, kb);
+      issue_x(s, kb);
       if (++kb == KB) { kb = 0; ++tile; }
       if (++s == stages) { s = 0; ph ^= 1u; }
     }
@@ -373,57 +357,36 @@ __global__ void __launch_bounds__(kDecodeThreads, 2)
     const uint32_t stage_x = stage_w + kTileM * 16u;
     const uint32_t kStagingSlot = static_cast<uint32_t>(kTileM + BN) * 16u;
     const bool has_x = r < p.Nk;
-    // One chunk of the fetch sequence; `what` selects W's bytes (1), X's bytes (2) or both (3).
-    struct Cursor {
-      int i, tile, kb;
-    };
-    auto fetch_chunk = [&](Cursor& f, int slot, int what) {
-      if (f.i >= n_units) return;
-      const int col = (f.kb * kSfBytes) >> 4;
-      if (what & 1) {
-        const int row = f.tile * kTileM + r;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    int f_i = 0, f_tile = tile0, f_kb = kb0;  // fetch cursor: the next chunk starts at this unit
+    auto fetch = [&](int slot) {
+      if (f_i < n_units) {
+        const int col = (f_kb * kSfBytes) >> 4;
+        const int row = f_tile * kTileM + r;
         const int valid_w = row < p.Mk ? min(16, p.kblocks32 - col * 16) : 0;
         const uint8_t* src_w = p.sw + static_cast<int64_t>(min(row, p.Mk - 1)) * p.ld_sw + col * 16;
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(stage_w + slot * kStagingSlot),
                      "l"(src_w), "r"(valid_w)
                      : "memory");
+        if (has_x) {
+          const uint8_t* src_x = p.sx + static_cast<int64_t>(r) * p.ld_sx + col * 16;
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(stage_x + slot * kStagingSlot),
+                       "l"(src_x), "r"(min(16, p.kblocks32 - col * 16))
+                       : "memory");
+        }
+        const int next_kb = (f_kb | (kUnitsPerChunk - 1)) + 1;
+        if (next_kb >= KB) {
+          f_i += KB - f_kb;
+          f_kb = 0;
+          ++f_tile;
+        } else {
+          f_i += next_kb - f_kb;
+          f_kb = next_kb;
+        }
       }
-      if ((what & 2) && has_x) {
-        const uint8_t* src_x = p.sx + static_cast<int64_t>(r) * p.ld_sx + col * 16;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(stage_x + slot * kStagingSlot),
-                     "l"(src_x), "r"(min(16, p.kblocks32 - col * 16))
-                     : "memory");
-      }
-      const int next_kb = (f.kb | (kUnitsPerChunk - 1)) + 1;
-      if (next_kb >= KB) {
-        f.i += KB - f.kb;
-        f.kb = 0;
-        ++f.tile;
-      } else {
-        f.i += next_kb - f.kb;
-        f.kb = next_kb;
-      }
-    };
-    Cursor fc{0, tile0, kb0};  // fetch cursor: the next chunk starts at this unit
-    auto fetch = [&](int slot) {
-      fetch_chunk(fc, slot, 3);
       asm volatile("cp.async.commit_group;" ::: "memory");  // always: the group count stays in step
     };
-    if (p.w_early) {
-      // immutable weights: W's bytes of the first chunks go out before the wait (they join
-      // the first group committed below, which is waited for before any chunk is used)
-      Cursor ahead = fc;
-      for (int j = 0; j < kDecodeFetchAhead; ++j) fetch_chunk(ahead, j, 1);
-    }
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (p.w_early) {
-      for (int j = 0; j < kDecodeFetchAhead; ++j) {
-        fetch_chunk(fc, j, 2);
-        asm volatile("cp.async.commit_group;" ::: "memory");
-      }
-    } else {
-      for (int j = 0; j < kDecodeFetchAhead; ++j) fetch(j);
-    }
+    for (int j = 0; j < kDecodeFetchAhead; ++j) fetch(j);
     int s = 0, kb = kb0, c_slot = 0;
     uint32_t ph = 0;
     uint4 cur_w = make_uint4(0, 0, 0, 0), cur_x = make_uint4(0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);

@@ -255,11 +255,6 @@ int init_device(int device, DeviceState** out) {
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
       CUDA_TRY(cudaFuncSetAttribute(decode_mx_kernel<kKindMxf4>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, st.smem_optin));
-      // all of the SM's L1 as shared memory, so that two decode CTAs can share an SM
-      CUDA_TRY(cudaFuncSetAttribute(decode_mx_kernel<kKindMxf8>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                    cudaSharedmemCarveoutMaxShared));
-      CUDA_TRY(cudaFuncSetAttribute(decode_mx_kernel<kKindMxf4>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                    cudaSharedmemCarveoutMaxShared));
       st.ready.store(true, std::memory_order_release);
     }
   }

@@ -217,7 +217,7 @@ class _Operator:
 
     def __init__(self, *, stream: Optional[int] = None, asynchronous: bool = False,
                  memory_space: int = _capi.MEM_AUTO, device: int = -1, tile_n: int = 0,
-                 pair: Optional[bool] = None, b_immutable: bool = False):
+                 pair: Optional[bool] = None):
         # A raw handle of 0 is CUDA's legacy default stream (what torch reports for its
         # default stream); the C ABI reserves NULL for "the library's own stream", so
         # pass the explicit legacy-stream handle instead.
@@ -228,9 +228,6 @@ class _Operator:
         self._tile_n = tile_n
         # testing/tuning: True/False force/forbid the two-CTA kernel, None lets the library decide
         self._pair_flag = 0 if pair is None else (_capi.FLAG_PAIR_ON if pair else _capi.FLAG_PAIR_OFF)
-        # the caller's promise that B (the weights) is not being written by work in flight
-        # (CPUOPS_B200_FLAG_B_IMMUTABLE): the small-m MX kernel may load it early
-        self._b_flag = _capi.FLAG_B_IMMUTABLE if b_immutable else 0
         self._gemm = _capi.load().cpuops_b200_gemm
 
     def run(self, desc: _capi.GemmDesc) -> Status:
@@ -251,7 +248,7 @@ class _Operator:
         desc.split_k_slices = int(args.split_k_slices)
         desc.memory_space = self._memory_space
         desc.stream = self._stream
-        desc.flags = (_capi.FLAG_ASYNC if self._async else 0) | self._pair_flag | self._b_flag
+        desc.flags = (_capi.FLAG_ASYNC if self._async else 0) | self._pair_flag
         desc.device = self._device
         desc.tile_n = self._tile_n
         return desc

@@ -89,12 +89,6 @@ enum { CPUOPS_B200_MEM_AUTO = 0, CPUOPS_B200_MEM_HOST = 1, CPUOPS_B200_MEM_DEVIC
  * of two CTAs per 256-row tile).  Neither flag: the library decides by problem size. */
 #define CPUOPS_B200_FLAG_PAIR_ON 2u
 #define CPUOPS_B200_FLAG_PAIR_OFF 4u
-/* The caller promises that B and its scales are not being written by any work still in
- * flight when this call is enqueued (the weights of a decode loop).  The small-m MX kernel
- * may then load its first tiles of B while the kernel before it in the stream is still
- * running; A, C and D keep ordinary stream order.  Without the flag every load waits for
- * that kernel.  Ignored by the other kernels. */
-#define CPUOPS_B200_FLAG_B_IMMUTABLE 8u
 
 typedef union cpuops_b200_scalar {
   int32_t i32; /* int8 path: alpha/beta/clamp bounds are s32 */

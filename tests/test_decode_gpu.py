@@ -109,20 +109,18 @@ def test_special_values_do_not_leak_between_rows(gpu, oracle):
     assert normwise(G[ok], R[ok]) <= MX_TOL
 
 
-@pytest.mark.parametrize("b_immutable", [False, True])
-def test_device_operands_async_back_to_back(gpu, oracle, b_immutable):
+def test_device_operands_async_back_to_back(gpu, oracle):
     """Device-resident operands, asynchronous calls back to back on one stream: each call's
-    CTAs may start while the call before it is still running, and with the weights declared
-    immutable (CPUOPS_B200_FLAG_B_IMMUTABLE) they load their first weight tiles before
-    that call has finished.  D of one call is never an input of the next here, but every
-    call rewrites the D buffers of the call three steps before it."""
+    CTAs may start while the call before it is still finishing.  D of one call is never an
+    input of the next here, but every call rewrites the D buffer of the call three steps
+    before it."""
     import torch
     m, n, k = 8, 14336 // 2, 4096
     probs = [W.mx_problem(FMT_E2M1, m, n, k, True, lds=128, seed=100 + i) for i in range(3)]
     dev = torch.device("cuda", 0)
     stream = torch.cuda.Stream(device=dev)
     op = c.GemmMx(STORAGE[FMT_E2M1], STORAGE[FMT_E2M1], layout(True), stream=stream.cuda_stream,
-                  asynchronous=True, memory_space=_capi.MEM_DEVICE, b_immutable=b_immutable)
+                  asynchronous=True, memory_space=_capi.MEM_DEVICE)
     bufs, outs = [], []
     with torch.cuda.stream(stream):
         for P in probs:
@@ -143,8 +141,7 @@ def test_device_operands_async_back_to_back(gpu, oracle, b_immutable):
         assert np.array_equal(t["D"].cpu().numpy().view(np.uint32), want.view(np.uint32))
 
 
-@pytest.mark.parametrize("b_immutable", [False, True])
-def test_a_call_may_consume_what_the_call_before_it_wrote(gpu, oracle, b_immutable):
+def test_a_call_may_consume_what_the_call_before_it_wrote(gpu, oracle):
     """Four calls back to back on one stream accumulate into one buffer (C = D, beta = 1):
     every call's epilogue reads what the previous call's epilogue wrote.  The kernels
     overlap at their edges (programmatic launch), so this is the ordering the device-side
@@ -155,7 +152,7 @@ def test_a_call_may_consume_what_the_call_before_it_wrote(gpu, oracle, b_immutab
     dev = torch.device("cuda", 0)
     stream = torch.cuda.Stream(device=dev)
     op = c.GemmMx(STORAGE[FMT_E4M3], STORAGE[FMT_E4M3], layout(True), stream=stream.cuda_stream,
-                  asynchronous=True, memory_space=_capi.MEM_DEVICE, b_immutable=b_immutable)
+                  asynchronous=True, memory_space=_capi.MEM_DEVICE)
     acc = torch.from_numpy(probs[0].C.copy()).to(dev)
     keep = []
     with torch.cuda.stream(stream):
