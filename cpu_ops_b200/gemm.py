@@ -77,6 +77,18 @@ def data_ptr(buf: Any) -> Optional[int]:
     return C.addressof(buf)
 
 
+def _settle_torch_operands(args) -> None:
+    """A call without a stream runs on the library's own stream, which is not ordered after
+    torch's: if an operand is a CUDA torch tensor, wait for torch's current stream first so
+    that fills and copies enqueued there have landed (the C ABI leaves this to the caller)."""
+    for ref in (args.ref_A, args.ref_B, args.ref_C, args.ref_D):
+        buf = getattr(ref, "data", None)
+        if getattr(buf, "is_cuda", False):
+            import torch
+            torch.cuda.current_stream(buf.device).synchronize()
+            return
+
+
 @dataclass
 class GemmCoord:
     """gemm_coord.h:6-13."""
@@ -241,7 +253,10 @@ class _Operator:
 
     def __call__(self, args, num_threads: int = 0) -> Status:
         del num_threads  # accepted for source compatibility; the GPU grid replaces the pool
-        return self.run(self.describe(args))
+        desc = self.describe(args)
+        if self._stream is None:
+            _settle_torch_operands(args)
+        return self.run(desc)
 
     def _finish(self, desc: _capi.GemmDesc, args) -> _capi.GemmDesc:
         desc.struct_size = C.sizeof(_capi.GemmDesc)

@@ -141,7 +141,10 @@ typedef struct cpuops_b200_gemm_desc {
   cpuops_b200_epilogue_op ops[CPUOPS_B200_MAX_OPS];
   int32_t split_k_slices;
   int32_t memory_space; /* CPUOPS_B200_MEM_* for all pointers (AUTO: ask the driver) */
-  void* stream;         /* cudaStream_t; NULL = the library's own stream             */
+  void* stream;         /* cudaStream_t; NULL = the library's own stream, which is not
+                           ordered after the caller's streams: device operands must be
+                           complete before the call (a synchronous call returns with D
+                           complete)                                                 */
   uint32_t flags;       /* CPUOPS_B200_FLAG_*                                        */
   int32_t device;       /* CUDA device ordinal, or -1 for the current device         */
   int32_t tile_n;       /* 0 = automatic; else force the N tile (testing/tuning)     */
