@@ -706,6 +706,16 @@ def run_sharded(args, rank, world, dev, lib, peaks, peak_kind):
             gemm_then_gather(i)
         torch.cuda.current_stream().wait_stream(side)
         with_gather_ms = timed(gathered(steps), steps)
+        # the same with 32 SMs left to the gather: the GEMM's persistent CTAs otherwise hold
+        # every SM until the kernel ends, and NCCL's kernel can only start after it
+        sm_total = torch.cuda.get_device_properties(dev).multi_processor_count
+        lib.cpuops_b200_set_sm_limit(-1, sm_total - 32)
+        for i in range(3):
+            gemm_then_gather(i)
+        torch.cuda.current_stream().wait_stream(side)
+        with_gather_margin_ms = timed(gathered(steps), steps)
+        gemm_margin_ms = timed(gemm, steps)
+        lib.cpuops_b200_set_sm_limit(-1, 0)
         gather_ms = timed(lambda i: dist.all_gather_into_tensor(d_full[0], d_blk[0]), steps)
 
         # ---- checks (not timed) ----
@@ -770,6 +780,13 @@ def run_sharded(args, rank, world, dev, lib, peaks, peak_kind):
                 "with_gather": {"ms_per_step": with_gather_ms,
                                 "tflops_aggregate": ops / (with_gather_ms / 1e3) / 1e12,
                                 "strong_scaling_efficiency": single_ms / (world * with_gather_ms)},
+                "with_gather_32_sms_left_to_nccl": {
+                    "ms_per_step": with_gather_margin_ms, "gemm_alone_ms_per_step": gemm_margin_ms,
+                    "tflops_aggregate": ops / (with_gather_margin_ms / 1e3) / 1e12,
+                    "strong_scaling_efficiency": single_ms / (world * with_gather_margin_ms),
+                    "how": "cpuops_b200_set_sm_limit(SMs - 32): the GEMM leaves 32 SMs free (NCCL's "
+                           "all-gather kernel is 32 CTAs wide here), so the gather of step i runs beside "
+                           "the GEMM of step i + 1"},
                 "gather_alone": {"ms": gather_ms, "bytes_received_per_rank": (world - 1) * blk_bytes,
                                  "nvlink_gbs_received_per_rank": (world - 1) * blk_bytes / (gather_ms / 1e3) / 1e9},
                 "parity_ok": bool(flags[0].item() == 1.0), "worst_sampled_normwise_error": float(-flags[1].item()),

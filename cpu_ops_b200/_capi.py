@@ -40,6 +40,7 @@ EXPORTED_SYMBOLS = (
     "cpuops_b200_scale_layout_bytes",
     "cpuops_b200_shard_rows",
     "cpuops_b200_stream_status",
+    "cpuops_b200_set_sm_limit",
     "cpuops_b200_set_wait_budget_us",
     "cpuops_b200_selftest_wait_timeout",
     "cpuops_b200_profile",
@@ -113,6 +114,8 @@ def load() -> C.CDLL:
                                            C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
     lib.cpuops_b200_stream_status.restype = C.c_int
     lib.cpuops_b200_stream_status.argtypes = [C.c_void_p]
+    lib.cpuops_b200_set_sm_limit.restype = C.c_int
+    lib.cpuops_b200_set_sm_limit.argtypes = [C.c_int32, C.c_int32]
     lib.cpuops_b200_set_wait_budget_us.restype = C.c_int
     lib.cpuops_b200_set_wait_budget_us.argtypes = [C.c_uint32]
     lib.cpuops_b200_selftest_wait_timeout.restype = C.c_int

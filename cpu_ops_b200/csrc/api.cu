@@ -169,7 +169,7 @@ DecodePlan plan_decode(const DeviceState& st, int kind, int Mk, int Nk, int k_bl
   int ctas_per_sm = 1;
   if (env_switches().decode_ctas_per_sm > 0) ctas_per_sm = env_switches().decode_ctas_per_sm;
   const int64_t units = static_cast<int64_t>(dp.tiles) * k_blocks;
-  const int cap = st.sm_count * ctas_per_sm;
+  const int cap = st.sms() * ctas_per_sm;
   int grid;
   if (never_split || 4 * dp.tiles >= cap) {
     // whole tiles per CTA: no partial sums.  (Measured on 112 tiles: cutting k to feed all
@@ -411,6 +411,14 @@ CPUOPS_B200_API int cpuops_b200_stream_status(void* stream) {
     CUDA_TRY(cudaStreamSynchronize(s));
     return CPUOPS_B200_STATUS_DEVICE_TIMEOUT;
   }
+  return 0;
+}
+
+CPUOPS_B200_API int cpuops_b200_set_sm_limit(int32_t device, int32_t sms) {
+  DeviceRestore restore;
+  DeviceState* st = nullptr;
+  if (int rc = init_device(device, &st)) return rc;
+  st->sm_limit.store(sms > 0 ? std::max(2, sms) : 0);
   return 0;
 }
 
@@ -670,6 +678,7 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
   }
   cudaStream_t stream = d->stream ? static_cast<cudaStream_t>(d->stream) : st.stream;
   const bool async = (d->flags & CPUOPS_B200_FLAG_ASYNC) != 0;
+  const int sms = st.sms();  // SMs this call may occupy (cpuops_b200_set_sm_limit)
 
   // ---- which pointers are host memory -------------------------------------------
   const bool a_dev = k == 0 || is_device_pointer(d->a, d->memory_space);
@@ -719,7 +728,7 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     } else if (Nk <= 128) {
       ch.BN = bk_role_mn ? 128 : pick_bn_for_small(Nk);
     } else {
-      ch.BN = pick_tile_width(Mk, Nk, k_blocks, is_mx, st.sm_count, beta_nonzero, bk_role_mn);
+      ch.BN = pick_tile_width(Mk, Nk, k_blocks, is_mx, sms, beta_nonzero, bk_role_mn);
     }
     if (ch.BN % 32 != 0 || ch.BN < 32 || ch.BN > 256 || (bk_role_mn && ch.BN % 128 != 0)) {
       set_error("tile_n %d is not usable here", ch.BN);
@@ -729,25 +738,25 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     const int64_t tiles = static_cast<int64_t>((Mk + 127) / 128) * ((Nk + ch.BN - 1) / ch.BN);
     if (d->split_k_slices > 1) {
       ch.slices = std::min(d->split_k_slices, k_blocks);
-    } else if (d->split_k_slices == 0 && tiles < 2 * st.sm_count && k_blocks >= 8) {
+    } else if (d->split_k_slices == 0 && tiles < 2 * sms && k_blocks >= 8) {
       // Few tiles and a deep k: cut k so that the work items fill the SMs.  Time
       // estimate (microseconds): waves x k-blocks per slice x per-block time, plus
       // the slab write + read and one more launch when split.
-      const double hbm_bytes_per_us = 6.0e6, per_sm = hbm_bytes_per_us / st.sm_count;
+      const double hbm_bytes_per_us = 6.0e6, per_sm = hbm_bytes_per_us / sms;
       const double block_us = std::max(gemm_stage_bytes(ch.BN) / per_sm,
                                        4.0 * std::max(ch.BN / 2.0, (128.0 + ch.BN) / 4.0) / 1500.0);
       double best = 1e300;
       // unsplit, a ragged last tile column is computed narrower and dealt out evenly:
       // rounds in units of a wide tile (feed-bound cost ~ 128 + width rows per k-block)
-      double rounds1 = static_cast<double>((tiles + st.sm_count - 1) / st.sm_count);
+      double rounds1 = static_cast<double>((tiles + sms - 1) / sms);
       {
         const int n_tiles = (Nk + ch.BN - 1) / ch.BN, m_tiles = (Mk + 127) / 128, last = last_tile_width(Nk, ch.BN);
         if (!bk_role_mn && n_tiles >= 2 && last < ch.BN && !env_switches().no_narrow)
-          rounds1 = busiest_worker(m_tiles * (n_tiles - 1), m_tiles, st.sm_count, 1.0,
+          rounds1 = busiest_worker(m_tiles * (n_tiles - 1), m_tiles, sms, 1.0,
                                    (128.0 + last) / (128.0 + ch.BN));
       }
       for (int s = 1; s <= std::min(32, k_blocks / 2); ++s) {
-        const int64_t waves = (tiles * s + st.sm_count - 1) / st.sm_count;
+        const int64_t waves = (tiles * s + sms - 1) / sms;
         const int per_slice = (k_blocks + s - 1) / s;
         double t_us = (s == 1 ? rounds1 : static_cast<double>(waves)) * per_slice * block_us;
         if (s > 1) t_us += 2.0 * s * Mk * static_cast<double>(Nk) * 4.0 / hbm_bytes_per_us + 3.0;
@@ -767,7 +776,7 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     const int Mk = ch.swap ? n : m, Nk = ch.swap ? m : n;
     const bool bk_role_mn = !(ch.swap ? a_kmajor : b_kmajor);
     const bool legal = Mk > 128 && (!bk_role_mn || ch.BN == 256) && ch.BN % 32 == 0;
-    bool want = pair_pays(Mk, Nk, k_blocks, ch.BN, ch.slices, st.sm_count, bk_role_mn);
+    bool want = pair_pays(Mk, Nk, k_blocks, ch.BN, ch.slices, sms, bk_role_mn);
     if (env_switches().pair >= 0) want = env_switches().pair != 0;
     if (d->flags & CPUOPS_B200_FLAG_PAIR_ON) want = true;
     if (d->flags & CPUOPS_B200_FLAG_PAIR_OFF) want = false;
@@ -974,7 +983,7 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
   const int ew_threads = 256;
   auto ew_blocks = [&](int64_t total) {
     return static_cast<unsigned>(std::max<int64_t>(
-        1, std::min<int64_t>((total + ew_threads - 1) / ew_threads, static_cast<int64_t>(st.sm_count) * 16)));
+        1, std::min<int64_t>((total + ew_threads - 1) / ew_threads, static_cast<int64_t>(sms) * 16)));
   };
 
   if (k == 0) {
@@ -1179,7 +1188,7 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     {
       // One wave of CTAs covers g m-tiles x (SMs / g) n-tiles; its L2 footprint per
       // k-block, g * 128 + (SMs / g) * BN rows, is smallest for g = sqrt(SMs * BN / 128).
-      int g = static_cast<int>(std::lround(std::sqrt(st.sm_count * ch.BN / 128.0))) / (ch.pair ? 2 : 1);
+      int g = static_cast<int>(std::lround(std::sqrt(sms * ch.BN / 128.0))) / (ch.pair ? 2 : 1);
       if (env_switches().raster_m > 0) g = env_switches().raster_m;
       p.raster_m = std::max(1, std::min(g, p.m_tiles));
     }
@@ -1252,7 +1261,7 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     int epi_warps = 4;
     {
       const int64_t items = static_cast<int64_t>(p.m_tiles) * p.n_tiles * p.slices;
-      if (!ch.pair && items <= st.sm_count && ch.BN >= 128) epi_warps = 8;
+      if (!ch.pair && items <= sms && ch.BN >= 128) epi_warps = 8;
       // ... or when k is so short that a tile's k loop (about 600 cycles per k-block) ends
       // well before four warps have drained the previous tile (about 1500 cycles per
       // 32-column chunk each): measured +10-15 % at K = 1024, nothing at K = 2048
@@ -1284,7 +1293,7 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     const int smem = std::max(gemm_smem_bytes(b_rows, stages, sf_stage_bytes, p.ring_bufs, epi_warps),
                               120 * 1024);
     const int64_t total_tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles * p.slices;
-    unsigned grid = static_cast<unsigned>(std::min<int64_t>(total_tiles, st.sm_count));
+    unsigned grid = static_cast<unsigned>(std::min<int64_t>(total_tiles, sms));
     CUtensorMap tmSFA = tmA, tmSFB = tmA;  // used by the pair kernel's scale loads only
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(epi_warps == 8 ? kGemmThreadsWide : kGemmThreads);
@@ -1323,7 +1332,8 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
         set_error("internal: two-CTA clusters cannot be launched on this device");
         return CPUOPS_B200_STATUS_CUDA_ERROR;
       }
-      grid = 2u * static_cast<unsigned>(std::min<int64_t>(total_tiles, st.pair_clusters[kind]));
+      grid = 2u * static_cast<unsigned>(
+                      std::min<int64_t>({total_tiles, static_cast<int64_t>(st.pair_clusters[kind]), sms / 2}));
       if (is_mx) {
         if (int rc = make_tensor_map_atoms(&tmSFA, p.sfa, sfa_bytes / 512, p.sfa_stage_bytes / 512)) return rc;
         if (int rc = make_tensor_map_atoms(&tmSFB, p.sfb, sfb_bytes / 512, p.sfb_stage_bytes / 512)) return rc;

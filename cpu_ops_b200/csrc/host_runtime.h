@@ -13,6 +13,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
@@ -83,6 +84,14 @@ struct DeviceState {
   std::atomic<bool> ready{false};
   int device = -1;
   int sm_count = 0;
+  // SMs the GEMM kernels may occupy (0: all).  A caller that runs a communication kernel
+  // beside the GEMM (an all-gather of D on another stream) leaves it a few SMs this way:
+  // the persistent kernels otherwise hold every SM until they end.
+  std::atomic<int> sm_limit{0};
+  int sms() const {
+    const int lim = sm_limit.load();
+    return lim > 0 ? std::min(lim, sm_count) : sm_count;
+  }
   int smem_optin = 0;
   cudaStream_t stream = nullptr;  // the library's own stream
   int32_t* error_dev = nullptr;   // device error word

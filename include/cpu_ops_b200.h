@@ -219,6 +219,14 @@ CPUOPS_B200_API int cpuops_b200_shard_rows(int32_t m, int32_t world, int32_t ran
 /* Status of work enqueued with FLAG_ASYNC on `stream` (synchronises it). */
 CPUOPS_B200_API int cpuops_b200_stream_status(void* stream);
 
+/* SMs the GEMM kernels of later calls on `device` (-1: the current one) may occupy; 0 or
+ * less = all of them (the default).  No counterpart in the reference.  The kernels are
+ * persistent, one CTA per SM, and hold their SMs until they end: a caller that wants a
+ * communication kernel to run beside a GEMM (the all-gather of D on a second stream) leaves
+ * it some SMs with this setting.  Results do not depend on it for int8; for MX it can change
+ * the automatic split-k choice like any change of problem size does. */
+CPUOPS_B200_API int cpuops_b200_set_sm_limit(int32_t device, int32_t sms);
+
 /* Budget of every bounded device-side wait (mbarrier waits of the GEMM kernels' roles), in
  * microseconds; 0 restores the default of one second.  A wait that runs out makes the
  * kernel record a code, unwind and return; the call (or cpuops_b200_stream_status for

@@ -134,3 +134,29 @@ def test_the_callers_current_device_is_left_alone(gpu, oracle):
     assert op(args) == c.Status.kSuccess, _capi.last_error()
     assert torch.cuda.current_device() == before
     assert normwise(D, run_mx_oracle(oracle, P, 1.0, 0.0)) <= MX_TOL
+
+
+def test_sm_limit_leaves_sms_free_and_changes_no_result(gpu, lib, oracle):
+    """cpuops_b200_set_sm_limit: the persistent kernels launch at most that many CTAs (so that
+    a communication kernel on another stream finds free SMs); the int8 result keeps its bits,
+    the MX result stays inside the tolerance, and 0 restores the default."""
+    P = W.int8_problem(2048, 2304, 1024, seed=61)          # 16 x 9 tiles: more than any limit below
+    Q = W.mx_problem(FMT_E4M3, 1536, 2048, 2048, True, seed=62)
+    want_i8 = run_int8_oracle(oracle, P, 1, 1)
+    want_mx = run_mx_oracle(oracle, Q, 1.0, 0.5)
+    try:
+        for limit in (64, 101, 132):
+            assert lib.cpuops_b200_set_sm_limit(-1, limit) == 0
+            st, D = run_int8_gpu(P, 1, 1)
+            assert st == c.Status.kSuccess, _capi.last_error()
+            assert _capi.last_plan().grid <= limit
+            assert np.array_equal(D, want_i8)
+            from tests.gpu_helpers import run_mx_gpu
+            st, D = run_mx_gpu(Q, 1.0, 0.5, split=1)
+            assert st == c.Status.kSuccess, _capi.last_error()
+            assert _capi.last_plan().grid <= limit
+            assert normwise(D, want_mx) <= MX_TOL
+    finally:
+        assert lib.cpuops_b200_set_sm_limit(-1, 0) == 0
+    st, D = run_int8_gpu(P, 1, 1)
+    assert st == c.Status.kSuccess and np.array_equal(D, want_i8)
