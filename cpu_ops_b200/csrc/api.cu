@@ -303,12 +303,12 @@ CPUOPS_B200_API int cpuops_b200_debug_clock(unsigned long long* out) {
 }
 
 // Instrumented build only: the decode kernel's role stamps of the last sixteen launches
-// (16 words each; see DECODE_STAMP), then clears them.
+// (32 words each; see DECODE_STAMP), then clears them.
 CPUOPS_B200_API int cpuops_b200_debug_decode_clock(unsigned long long* out, int32_t* launches) {
   if (!g_decode_clk || !out) return 1;
   cudaDeviceSynchronize();
-  cudaMemcpy(out, g_decode_clk, 16 * 16 * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
-  cudaMemset(g_decode_clk, 0, 16 * 16 * sizeof(unsigned long long));
+  cudaMemcpy(out, g_decode_clk, 16 * 32 * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+  cudaMemset(g_decode_clk, 0, 16 * 32 * sizeof(unsigned long long));
   if (launches) *launches = static_cast<int32_t>(g_decode_clk_launch);
   g_decode_clk_launch = 0;
   return 0;
@@ -370,9 +370,18 @@ static int launch_relayout(const void* src0, void* dst0, const ScaleLayout& L0, 
   if (src1) items += relayout_work_items(L1);
   const int threads = 128;
   const int64_t blocks = std::min<int64_t>((items * 32 + threads - 1) / threads, 148 * 16);
-  relayout_scales_kernel<<<static_cast<unsigned>(std::max<int64_t>(blocks, 1)), threads, 0, stream>>>(
-      static_cast<const uint8_t*>(src0), static_cast<uint8_t*>(dst0), L0,
-      static_cast<const uint8_t*>(src1), static_cast<uint8_t*>(dst1), L1);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(std::max<int64_t>(blocks, 1)));
+  cfg.blockDim = dim3(threads);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = env_switches().no_pdl ? 0 : 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  CUDA_TRY(cudaLaunchKernelEx(&cfg, relayout_scales_kernel, static_cast<const uint8_t*>(src0),
+                              static_cast<uint8_t*>(dst0), L0, static_cast<const uint8_t*>(src1),
+                              static_cast<uint8_t*>(dst1), L1));
   g_launches.fetch_add(1);
   CUDA_TRY(cudaGetLastError());
   return 0;
@@ -1034,14 +1043,14 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
     q.error = st.error_dev;
 #ifdef CPUOPS_B200_INSTRUMENT
     if (env_switches().clk) {
-      // sixteen launches' worth of stamps, one block of 16 words per launch in turn; the
+      // sixteen launches' worth of stamps, one block of 32 words per launch in turn; the
       // buffer is cleared when it is read (cpuops_b200_debug_decode_clock), never between
       // launches, so that consecutive launches stay adjacent in the stream
       if (!g_decode_clk) {
-        cudaMalloc(&g_decode_clk, 16 * 16 * sizeof(unsigned long long));
-        cudaMemset(g_decode_clk, 0, 16 * 16 * sizeof(unsigned long long));
+        cudaMalloc(&g_decode_clk, 16 * 32 * sizeof(unsigned long long));
+        cudaMemset(g_decode_clk, 0, 16 * 32 * sizeof(unsigned long long));
       }
-      q.clk = g_decode_clk + 16 * (g_decode_clk_launch++ % 16);
+      q.clk = g_decode_clk + 32 * (g_decode_clk_launch++ % 16);
       static bool told = false;
       if (!told) {
         told = true;
@@ -1347,12 +1356,12 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
       CUDA_TRY(cudaEventCreate(&ev1));
       CUDA_TRY(cudaEventRecord(ev0, stream));
     }
-    if (is_mx && !profile) {
-      // MX: the scale re-layout kernel is the launch just before this one.  Programmatic
-      // stream serialization lets this kernel's CTAs start (barriers, tensor memory,
-      // descriptor prefetch) while that one is still running; the producer thread waits
-      // for it before the first scale load.  (Not while profiling: the timing events sit
-      // between the two launches.)
+    if (!profile && !env_switches().no_pdl) {
+      // Programmatic stream serialization lets this kernel's CTAs start (barriers, tensor
+      // memory, descriptor prefetch) while the kernel before it in the stream -- for MX the
+      // scale re-layout kernel -- is still running; the producer and epilogue warps wait for
+      // it before they touch global memory.  (Not while profiling: the timing events sit
+      // between the launches.)
       attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
       attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
       ++n_attr;

@@ -117,6 +117,9 @@ __global__ void relayout_scales_kernel(const uint8_t* __restrict__ src0, uint8_t
                                        ScaleLayout L0, const uint8_t* __restrict__ src1,
                                        uint8_t* __restrict__ dst1, ScaleLayout L1) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // launched with programmatic stream serialization itself: the GEMM before it may still be
+  // reading the atoms this kernel is about to overwrite
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int64_t items0 = relayout_work_items(L0);
   const int64_t items1 = src1 ? relayout_work_items(L1) : 0;
   const int lane = threadIdx.x & 31;

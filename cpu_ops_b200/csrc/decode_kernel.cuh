@@ -435,6 +435,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 1)
     const int q = warp & 3;  // the TMEM lane quarter this warp can read
     const int nchunks = BN / 32;
     const EpilogueParams& e = p.epi;
+    warm_epilogue_params(e);
+    asm volatile("" ::"r"(p.Mk ^ p.Nk ^ p.max_pieces), "l"(p.partial), "l"(p.counters));
     int buf = 0, kb = kb0, tile = tile0, i = 0;
     uint32_t acc_ph = 0;
     while (i < n_units) {
@@ -465,15 +467,18 @@ __global__ void __launch_bounds__(kDecodeThreads, 1)
         uint32_t r[32];
         tmem_ld_32x32(taddr + static_cast<uint32_t>(c * 32), r);
         tmem_ld_wait();
+        if (i + piece_units == n_units && c == 0) DECODE_STAMP(p, 8, warp == 6 && lane == 0);
         if (c + 1 == nchunks) {
           // the accumulator is in registers: hand the buffer back to the MMA warp
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(acc_empty_bar(buf));
         }
+        if (i + piece_units == n_units && c == 0) DECODE_STAMP(p, 9, warp == 6 && lane == 0);
         const int kcol0 = c * 32, ncols = min(32, p.Nk - kcol0);
         if (whole) {
           if (krow < p.Mk && ncols > 0) decode_store_chunk(e, r, krow, kcol0, ncols);
+          if (i + piece_units == n_units && c == 0) DECODE_STAMP(p, 10, warp == 6 && lane == 0);
         } else {
           // raw partial sums, column by column: a warp writes 128 contiguous bytes per column
 #pragma unroll

@@ -155,6 +155,22 @@ __device__ __forceinline__ void apply_op_chunk(const EpilogueOp& op, uint32_t (&
   }
 }
 
+// Reads every field of the epilogue parameters once.  Kernel parameters live in constant
+// memory, and a field's first read on an SM misses the constant cache (measured: about
+// 0.6 us).  The epilogue warps call this while they are still waiting for their first
+// accumulator, so that the misses are not paid between the last MMA and the first store.
+__device__ __forceinline__ void warm_epilogue_params(const EpilogueParams& e) {
+  uint32_t sink = e.alpha ^ e.beta ^ static_cast<uint32_t>(e.beta_nonzero) ^ static_cast<uint32_t>(e.activation) ^
+                  static_cast<uint32_t>(e.n_ops) ^ static_cast<uint32_t>(reinterpret_cast<uintptr_t>(e.D)) ^
+                  static_cast<uint32_t>(reinterpret_cast<uintptr_t>(e.C)) ^ static_cast<uint32_t>(e.d_sr) ^
+                  static_cast<uint32_t>(e.d_sc) ^ static_cast<uint32_t>(e.c_sr) ^ static_cast<uint32_t>(e.c_sc);
+#pragma unroll
+  for (int t = 0; t < kMaxOps; ++t)
+    sink ^= static_cast<uint32_t>(e.ops[t].opcode) ^ static_cast<uint32_t>(reinterpret_cast<uintptr_t>(e.ops[t].ptr)) ^
+            e.ops[t].lo ^ e.ops[t].hi;
+  asm volatile("" ::"r"(sink));
+}
+
 // One element, all steps (used by the split-k reduce and k == 0 kernels).
 template <bool kInt>
 __device__ __forceinline__ uint32_t epilogue_element(const EpilogueParams& e, uint32_t acc,

@@ -189,6 +189,10 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
   constexpr bool kInt = (KIND == kKindI8);
   constexpr bool kMx = !kInt;
   constexpr int kCtas = kPair ? 2 : 1;
+  // Programmatic dependent launch: the next kernel in the stream may become resident as
+  // this one's CTAs retire; in return every role of this kernel that touches global memory
+  // first waits for the kernel before it (griddepcontrol.wait), so stream order holds.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const uint32_t cta_rank = kPair ? cluster_cta_rank() : 0u;
   const bool leader = cta_rank == 0;
   const int work0 = static_cast<int>(blockIdx.x) / kCtas;      // first work item of this CTA (pair)
@@ -311,9 +315,9 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
       const int a_mn = p.a_mn_major, b_mn = p.b_mn_major, b_chunks = b_rows / 128;
       const int sfa_atoms_ld = p.sfa_stage_bytes / 512, sfb_atoms_ld = p.sfb_stage_bytes / 512;
       const uint32_t sfa_bytes = p.sfa_stage_bytes, sfb_bytes = p.sfb_stage_bytes;
-      // The scale atoms come from the re-layout kernel launched just before this one,
-      // which may still be running (programmatic stream serialization).
-      if constexpr (kMx) asm volatile("griddepcontrol.wait;" ::: "memory");
+      // The kernel before this one in the stream may still be running (programmatic stream
+      // serialization): for MX it is the re-layout kernel that writes the scale atoms.
+      asm volatile("griddepcontrol.wait;" ::: "memory");
       const bool pdbg = B200_CLK(p) != nullptr && blockIdx.x == 0;
       long long pdbg_wait = 0;
       const long long pdbg_start = pdbg ? clock64() : 0;
@@ -569,6 +573,9 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
     // A third buffer (p.ring_bufs == 3) hides that wait at the price of shared memory.
     const bool ring = p.c_ring != 0, d_tma = p.d_tma != 0;
     const uint32_t nb = static_cast<uint32_t>(p.ring_bufs);
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // before C is read, D or a slab written
+    warm_epilogue_params(p.epi);  // constant-cache misses now, not after the first accumulator
+    asm volatile("" ::"r"(p.Mk ^ p.Nk ^ p.mode), "l"(p.ws), "l"(p.ws_slab ^ p.ws_sr ^ p.ws_sc));
     const uint32_t my_c = c_base + static_cast<uint32_t>(ew) * nb * 4096u;
     uint32_t cq = 0;        // chunks consumed so far by this warp
     uint32_t cq_b = 0, cq_ph = 0;  // its buffer and that buffer's barrier parity
