@@ -41,6 +41,9 @@
 //
 // Roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer (owns tensor memory), warps
 // 2-5 scale writers (thread = tile row), warps 6-9 epilogue (one TMEM lane quarter each).
+// A stage's "full" barrier collects the TMA bytes and the four writer warps' arrivals, so
+// the MMA warp waits once per stage; the writers handle the units of one 16-byte scale
+// fetch together (one proxy fence per fetch, not per unit).
 // Every wait is bounded, as in the general kernel.
 #pragma once
 
@@ -168,12 +171,11 @@ __global__ void __launch_bounds__(kDecodeThreads, 1)
   const uint32_t staging_base = atom_base + stages * atom_bytes;
   const uint32_t bar_base = staging_base + static_cast<uint32_t>(decode_staging_bytes(BN));
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto ready_bar = [&](int s) { return bar_base + 8u * (kDecodeMaxStages + s); };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (2 * kDecodeMaxStages + s); };
-  auto acc_full_bar = [&](int b) { return bar_base + 8u * (3 * kDecodeMaxStages + b); };
-  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (3 * kDecodeMaxStages + 2 + b); };
-  const uint32_t drain_bar = bar_base + 8u * (3 * kDecodeMaxStages + 4);
-  constexpr int kBarriers = 3 * kDecodeMaxStages + 5;
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kDecodeMaxStages + s); };
+  auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * kDecodeMaxStages + b); };
+  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * kDecodeMaxStages + 2 + b); };
+  const uint32_t drain_bar = bar_base + 8u * (2 * kDecodeMaxStages + 4);
+  constexpr int kBarriers = 2 * kDecodeMaxStages + 5;
   static_assert(8 * kBarriers + 8 <= kDecodeBarrierBytes, "barrier region too small");
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + (bar_base - smem_base) + 8 * kBarriers);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -188,12 +190,13 @@ __global__ void __launch_bounds__(kDecodeThreads, 1)
 
   if (warp == 2) {
     for (int i = lane; i < kBarriers; i += 32) {
-      // full: the producer's arrive.expect_tx; ready: one arrival per scale-writer warp;
-      // empty / accumulator full / drain: one tcgen05.commit; accumulator empty: one arrival
-      // per epilogue warp
+      // full: the producer's arrive.expect_tx plus one arrival per scale-writer warp (the
+      // phase completes when the operand tiles have landed AND the stage's atoms are
+      // written: one wait for the MMA warp); empty / accumulator full / drain: one
+      // tcgen05.commit; accumulator empty: one arrival per epilogue warp
       uint32_t count = 1u;
-      if (i >= kDecodeMaxStages && i < 2 * kDecodeMaxStages) count = 4u;
-      if (i == 3 * kDecodeMaxStages + 2 || i == 3 * kDecodeMaxStages + 3) count = 4u;
+      if (i < kDecodeMaxStages) count = 5u;
+      if (i == 2 * kDecodeMaxStages + 2 || i == 2 * kDecodeMaxStages + 3) count = 4u;
       mbar_init(bar_base + 8u * static_cast<uint32_t>(i), count);
     }
     if (lane == 0) *abort_flag = 0;
@@ -292,10 +295,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 1)
       const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
       uint32_t accumulate = 0;
       for (int j = 0; j < piece_units; ++j) {
-        // the stage's scale atoms are written and its operand tiles have landed
-        const bool got = mbar_wait_bounded(ready_bar(s), ph, abort_flag, budget_ns) &&
-                         mbar_wait_bounded(full_bar(s), ph, abort_flag, budget_ns);
-        if (!__all_sync(kAll, got)) {
+        // the stage's operand tiles have landed and its scale atoms are written
+        if (!__all_sync(kAll, mbar_wait_bounded(full_bar(s), ph, abort_flag, budget_ns))) {
           if (el) {
             atomicCAS(p.error, 0, kErrMmaWaitFull);
             *abort_flag = 1;
@@ -387,46 +388,60 @@ __global__ void __launch_bounds__(kDecodeThreads, 1)
       asm volatile("cp.async.commit_group;" ::: "memory");  // always: the group count stays in step
     };
     for (int j = 0; j < kDecodeFetchAhead; ++j) fetch(j);
-    int s = 0, kb = kb0, c_slot = 0;
+    int s = 0, kb = kb0, c_slot = 0, i = 0;
     uint32_t ph = 0;
     uint4 cur_w = make_uint4(0, 0, 0, 0), cur_x = make_uint4(0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
-    for (int i = 0; i < n_units; ++i) {
-      const bool new_chunk = i == 0 || (kb & (kUnitsPerChunk - 1)) == 0;
-      if (new_chunk) {
-        asm volatile("cp.async.wait_group %0;" ::"n"(kDecodeFetchAhead - 1) : "memory");
+    bool alive = true;
+    while (i < n_units && alive) {
+      // one chunk: the units that share this 16-byte fetch (up to the tile's and the range's end)
+      const int in_chunk = min(min(kUnitsPerChunk - (kb & (kUnitsPerChunk - 1)), KB - kb), n_units - i);
+      asm volatile("cp.async.wait_group %0;" ::"n"(kDecodeFetchAhead - 1) : "memory");
+      asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(cur_w.x), "=r"(cur_w.y), "=r"(cur_w.z), "=r"(cur_w.w)
+                   : "r"(stage_w + c_slot * kStagingSlot));
+      if (has_x)
         asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                     : "=r"(cur_w.x), "=r"(cur_w.y), "=r"(cur_w.z), "=r"(cur_w.w)
-                     : "r"(stage_w + c_slot * kStagingSlot));
-        if (has_x)
-          asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                       : "=r"(cur_x.x), "=r"(cur_x.y), "=r"(cur_x.z), "=r"(cur_x.w)
-                       : "r"(stage_x + c_slot * kStagingSlot));
-      }
-      // the stage's previous atoms have been copied to tensor memory (its MMAs are done)
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(empty_bar(s), ph ^ 1u, abort_flag, budget_ns))) {
-        if (lane == 0) {
-          atomicCAS(p.error, 0, kErrProducerWait);
-          *abort_flag = 1;
+                     : "=r"(cur_x.x), "=r"(cur_x.y), "=r"(cur_x.z), "=r"(cur_x.w)
+                     : "r"(stage_x + c_slot * kStagingSlot));
+      int s2 = s;
+      uint32_t ph2 = ph;
+      for (int u = 0; u < in_chunk; ++u) {
+        // the stage's previous atoms have been copied to tensor memory (its MMAs are done)
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(empty_bar(s2), ph2 ^ 1u, abort_flag, budget_ns))) {
+          if (lane == 0) {
+            atomicCAS(p.error, 0, kErrProducerWait);
+            *abort_flag = 1;
+          }
+          alive = false;
+          break;
         }
-        break;
-      }
-      const int sub = (kb & (kUnitsPerChunk - 1)) * kKa;  // first word of this unit within the chunk
-      const uint32_t aw = atom_base + s * atom_bytes + slot_off, ax = aw + kKa * 512u;
+        const int sub = ((kb + u) & (kUnitsPerChunk - 1)) * kKa;  // first word of this unit within the chunk
+        const uint32_t aw = atom_base + s2 * atom_bytes + slot_off, ax = aw + kKa * 512u;
 #pragma unroll
-      for (int a = 0; a < kKa; ++a) {
-        asm volatile("st.shared.u32 [%0], %1;" ::"r"(aw + 512u * a), "r"(pick_word(cur_w, sub + a)) : "memory");
-        asm volatile("st.shared.u32 [%0], %1;" ::"r"(ax + 512u * a), "r"(pick_word(cur_x, sub + a)) : "memory");
+        for (int a = 0; a < kKa; ++a) {
+          asm volatile("st.shared.u32 [%0], %1;" ::"r"(aw + 512u * a), "r"(pick_word(cur_w, sub + a)) : "memory");
+          asm volatile("st.shared.u32 [%0], %1;" ::"r"(ax + 512u * a), "r"(pick_word(cur_x, sub + a)) : "memory");
+        }
+        if (++s2 == stages) { s2 = 0; ph2 ^= 1u; }
       }
-      fence_proxy_async_shared_cta();  // these writes -> visible to tcgen05.cp
+      if (!alive) break;
+      fence_proxy_async_shared_cta();  // these writes -> visible to tcgen05.cp (one fence per chunk)
       __syncwarp();
-      if (lane == 0) mbar_arrive(ready_bar(s));
-      if (new_chunk) {
-        // the chunk is in registers (the stores above used it): its slot takes the next fetch
-        fetch(c_slot);
-        if (++c_slot == kDecodeFetchAhead) c_slot = 0;
+      if (lane == 0) {
+        int s3 = s;
+        for (int u = 0; u < in_chunk; ++u) {
+          mbar_arrive(full_bar(s3));
+          if (++s3 == stages) s3 = 0;
+        }
       }
-      if (++kb == KB) kb = 0;
-      if (++s == stages) { s = 0; ph ^= 1u; }
+      // the chunk is in registers (the stores above used it): its slot takes the next fetch
+      fetch(c_slot);
+      if (++c_slot == kDecodeFetchAhead) c_slot = 0;
+      s = s2;
+      ph = ph2;
+      i += in_chunk;
+      kb += in_chunk;
+      if (kb == KB) kb = 0;
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
   } else {
