@@ -1298,6 +1298,8 @@ static int gemm_body(const cpuops_b200_gemm_desc* d, int depth) {
       return CPUOPS_B200_STATUS_CUDA_ERROR;
     }
     p.stages = stages;
+    p.producers = stages >= 4 ? 2 : 1;
+    if (env_switches().producers == 1 || (env_switches().producers == 2 && stages >= 2)) p.producers = env_switches().producers;
     // At least 120 KB so that two CTAs never share an SM: each allocates all of tensor memory.
     const int smem = std::max(gemm_smem_bytes(b_rows, stages, sf_stage_bytes, p.ring_bufs, epi_warps),
                               120 * 1024);
@@ -1668,6 +1670,7 @@ CPUOPS_B200_API int cpuops_b200_gemm_i8_noalloc(const cpuops_b200_gemm_desc* d) 
   const int per_stage = gemm_stage_bytes(BN);
   int stages = std::min({(nd->smem_optin - 1024 - kBarrierBytes) / per_stage, kMaxStages, std::max(2, k_blocks)});
   p.stages = stages;
+  p.producers = stages >= 4 ? 2 : 1;
   const int smem = std::max(gemm_smem_bytes(BN, stages, 0), 120 * 1024);
   const int64_t total_tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles * p.slices;
   const unsigned grid = static_cast<unsigned>(std::min<int64_t>(total_tiles, nd->sm_count));

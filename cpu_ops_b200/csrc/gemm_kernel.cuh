@@ -38,8 +38,8 @@
 
 namespace b200 {
 
-constexpr int kGemmThreads = 192;      // producer, MMA issuer, 4 epilogue warps
-constexpr int kGemmThreadsWide = 320;  // ... or 8 epilogue warps, two per TMEM lane quarter
+constexpr int kGemmThreads = 224;      // producer, MMA issuer, 4 epilogue warps, second producer
+constexpr int kGemmThreadsWide = 352;  // ... or 8 epilogue warps, two per TMEM lane quarter
 constexpr uint32_t kTmemCols = 512;
 
 struct TileCoord {
@@ -218,7 +218,8 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
   const uint32_t c_base = (sf_base + stages * sf_stage + 1023u) & ~1023u;
   // Epilogue warps: 4, or 8 when launched with kGemmThreadsWide threads (two per TMEM lane
   // quarter, which take alternate 32-column chunks of the tile).
-  const int n_epi = static_cast<int>(blockDim.x >> 5) - 2;
+  const int n_epi = static_cast<int>(blockDim.x >> 5) - 3;
+  const int warp_producer2 = 2 + n_epi;  // the last warp
   const uint32_t bar_base =
       p.ring_bufs ? c_base + ring_bytes(p.ring_bufs, n_epi) : sf_base + stages * sf_stage;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -297,13 +298,20 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
     dbg_t0 = global_timer_ns();
   }
 
-  if (warp == 0) {
-    // ------------------------------ TMA producer ------------------------------
+  if (warp == 0 || warp == warp_producer2) {
+    // ------------------------------ TMA producers -----------------------------
     // The whole warp runs the loop; one elected lane issues (see the MMA issuer below).
-    {
+    // A k-block's trip (probe the stage's barrier, arm it, two to four loads) is a chain of
+    // dependent instruction latencies of about 600 cycles in a CTA pair - longer than the
+    // k-block's MMAs - so two producer warps take alternate k-blocks (p.producers == 2):
+    // producer j owns the k-blocks whose running index is j modulo 2, i.e. every second
+    // ring stage in turn.  Each stage is still armed and loaded by exactly one warp.
+    const int np = p.producers, me = warp == 0 ? 0 : 1;
+    if (me < np) {
       const uint32_t el = elect_one() ? 1u : 0u;
-      int s = 0;
+      int s = me;  // np <= stages
       uint32_t ph = 0, armed = 0, armed_parity = 0, peek = 0;
+      int g_par = 0;  // running k-block index at the start of the tile, modulo np
       bool ok = true;
       // (a packed 4-bit operand of a mixed-format GEMM credits only its 64 data bytes per
       // 128-byte shared-memory row, so the count comes from the launcher)
@@ -311,14 +319,13 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
       // pair: every load of both CTAs credits the leader's barrier, which alone is armed
       // (by the leader's producer) with the bytes of both
       const uint32_t full0 = kPair ? map_to_cta(full_bar(0), 0) : full_bar(0), empty0 = empty_bar(0);
-      uint32_t full_addr = full0, empty_addr = empty0, a_dst = smem_base, sf_dst = sf_base;
       const int a_mn = p.a_mn_major, b_mn = p.b_mn_major, b_chunks = b_rows / 128;
       const int sfa_atoms_ld = p.sfa_stage_bytes / 512, sfb_atoms_ld = p.sfb_stage_bytes / 512;
       const uint32_t sfa_bytes = p.sfa_stage_bytes, sfb_bytes = p.sfb_stage_bytes;
       // The kernel before this one in the stream may still be running (programmatic stream
       // serialization): for MX it is the re-layout kernel that writes the scale atoms.
       asm volatile("griddepcontrol.wait;" ::: "memory");
-      const bool pdbg = B200_CLK(p) != nullptr && blockIdx.x == 0;
+      const bool pdbg = B200_CLK(p) != nullptr && blockIdx.x == 0 && me == 0;
       long long pdbg_wait = 0;
       const long long pdbg_start = pdbg ? clock64() : 0;
       for (int t = work0; t < total_tiles && ok; t += work_step) {
@@ -327,14 +334,17 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
         const int m0 = m_tile128 * kTileM;
         // this CTA's B rows: its half of the width the tile is computed at
         const int n0 = tc.n_tile * p.BN + static_cast<int>(cta_rank) * (tc.bn / kCtas);
-        int kx = tc.kb0 * 128;  // k coordinate (bytes along k) of the next block
         const uint8_t* sfa_base = nullptr;  // this tile's scale atoms, k-block 0
         const uint8_t* sfb_base = nullptr;
         if constexpr (kMx) {
           sfa_base = p.sfa + static_cast<int64_t>(m_tile128) * p.k_blocks * p.sfa_stage_bytes;
           sfb_base = p.sfb + static_cast<int64_t>(tc.n_tile) * p.k_blocks * p.sfb_stage_bytes;
         }
-        for (int i = 0; i < tc.nkb; ++i, kx += 128) {
+        const int i0 = np == 1 ? 0 : ((me ^ g_par) & 1);  // this warp's first k-block of the tile
+        int kx = (tc.kb0 + i0) * 128;                     // k coordinate (bytes along k) of the next block
+        for (int i = i0; i < tc.nkb; i += np, kx += 128 * np) {
+          const uint32_t full_addr = full0 + 8u * s, empty_addr = empty0 + 8u * s;
+          const uint32_t a_dst = smem_base + s * stage_bytes, sf_dst = sf_base + s * sf_stage;
           const long long pw0 = pdbg ? clock64() : 0;
           if (!peek && !__all_sync(0xffffffffu, mbar_wait_bounded(empty_addr, ph ^ 1u, abort_flag, budget_ns))) {
             if (el) record_error(p, abort_flag, kErrProducerWait);
@@ -342,12 +352,15 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
             break;
           }
           if (pdbg) pdbg_wait += clock64() - pw0;
-          {
-            // probe the next stage's barrier now; the answer is used on the next trip
-            const bool wrap = s + 1 == stages;
-            peek = __all_sync(0xffffffffu, mbar_test_wait(wrap ? empty0 : empty_addr + 8,
-                                                         (wrap ? (ph ^ 1u) : ph) ^ 1u)) ? 1u : 0u;
+          // this warp's next stage and its parity
+          int sn = s + np;
+          uint32_t phn = ph;
+          if (sn >= stages) {
+            sn -= stages;
+            phn ^= 1u;
           }
+          // probe the next stage's barrier now; the answer is used on the next trip
+          peek = __all_sync(0xffffffffu, mbar_test_wait(empty0 + 8u * sn, phn ^ 1u)) ? 1u : 0u;
           if (leader) {
             mbar_expect_tx_p(full_bar(s), tx_bytes * kCtas, el);
             armed |= 1u << s;
@@ -378,20 +391,10 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
                           el);
             }
           }
-          if (++s == stages) {
-            s = 0;
-            ph ^= 1u;
-            full_addr = full0;
-            empty_addr = empty0;
-            a_dst = smem_base;
-            sf_dst = sf_base;
-          } else {
-            full_addr += 8;
-            empty_addr += 8;
-            a_dst += stage_bytes;
-            sf_dst += sf_stage;
-          }
+          s = sn;
+          ph = phn;
         }
+        g_par = (g_par + tc.nkb) & 1;
       }
       if (pdbg && el) {
         B200_CLK(p)[10] = static_cast<unsigned long long>(clock64() - pdbg_start);
@@ -560,6 +563,7 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
     __syncwarp();
   } else {
     // -------------------------------- epilogue --------------------------------
+    // (warps 2 .. 2 + n_epi - 1; the second producer warp took the first branch)
     const int q = warp & 3;   // the TMEM lane quarter this warp can read
     const int ew = warp - 2;  // index among the epilogue warps: its ring and its C barriers
     // with 8 epilogue warps the two of a quarter take alternate chunks: c0, c0 + cstep, ...

@@ -81,6 +81,7 @@ struct GemmParams {
   int32_t tx_operand_bytes; // bytes the A and B loads of one stage credit to the barrier, per CTA
   int32_t* error;           // device error word
   uint32_t wait_budget_us;  // budget of every bounded device-side wait
+  int32_t producers;        // TMA producer warps that share the k-blocks in turn (1 or 2)
 #ifdef CPUOPS_B200_INSTRUMENT
   unsigned long long* clk_dbg;  // instrumented build: {SM cycles, nanoseconds} of CTA 0
 #endif

@@ -360,11 +360,12 @@ struct EnvSwitches {
   int decode_grid = geti("CPUOPS_B200_DECODE_GRID", 0);
   int decode_stages = geti("CPUOPS_B200_DECODE_STAGES", 0);
   int decode_ctas_per_sm = geti("CPUOPS_B200_DECODE_CTAS_PER_SM", 0);
+  int producers = geti("CPUOPS_B200_PRODUCERS", 0);
 #else
   static constexpr bool no_c_ring = false, no_d_tma = false, clk = false, no_narrow = false,
                         no_decode = false, no_pdl = false;
   static constexpr int panels = 0, raster_m = 0, pair = -1, ring = 0, epi_warps = 0, decode_grid = 0,
-                       decode_stages = 0, decode_ctas_per_sm = 0;
+                       decode_stages = 0, decode_ctas_per_sm = 0, producers = 0;
 #endif
 };
 const EnvSwitches& env_switches() {
