@@ -359,8 +359,9 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
             sn -= stages;
             phn ^= 1u;
           }
-          // probe the next stage's barrier now; the answer is used on the next trip
-          peek = __all_sync(0xffffffffu, mbar_test_wait(empty0 + 8u * sn, phn ^ 1u)) ? 1u : 0u;
+          // probe the next stage's barrier now; the answer is read after this trip's loads
+          // have been issued and used on the next trip
+          const uint32_t probe = mbar_test_wait(empty0 + 8u * sn, phn ^ 1u);
           if (leader) {
             mbar_expect_tx_p(full_bar(s), tx_bytes * kCtas, el);
             armed |= 1u << s;
@@ -391,6 +392,7 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
                           el);
             }
           }
+          peek = __all_sync(0xffffffffu, probe != 0) ? 1u : 0u;
           s = sn;
           ph = phn;
         }
@@ -488,11 +490,11 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
             break;
           }
           if (dbg) dbg_wait_full += clock64() - tw0;
-          // probe the next ring slot now; the answer is consumed after this k-block's
-          // MMAs have been issued
+          // probe the next ring slot now; the answer (a shared-memory round trip of about
+          // 100 cycles) is only read after this k-block's MMAs have been issued
           const uint32_t nfull = (s + 1 == stages) ? full0 : full_addr + 8;
           const uint32_t nph = (s + 1 == stages) ? (ph ^ 1u) : ph;
-          peek = __all_sync(kAll, mbar_test_wait(nfull, nph)) ? 1u : 0u;
+          const uint32_t probe = mbar_test_wait(nfull, nph);
           const uint32_t sfb_t = sfa_t + 4u * sfa_atoms;
           tc_fence_after_sync();
           if constexpr (kMx) {
@@ -519,6 +521,7 @@ __global__ void __launch_bounds__(kGemmThreadsWide, 1)
           }
           accumulate = 1u;
           tc_commit_both<kPair>(empty_addr, el);  // frees the stage (in both CTAs) once these MMAs have read it
+          peek = __all_sync(kAll, probe != 0) ? 1u : 0u;
           if constexpr (kMx) {
             sfa_t += sf_cols;
             if (++sf_q == sf_slots) {
