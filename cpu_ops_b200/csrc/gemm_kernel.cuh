@@ -5,15 +5,17 @@
 // mma_policy_mx.h:171-257 + arch/mma_atom.h:29-38) and its tile store
 // (block_gemm.h:119-150).
 //
-// Structure: persistent, warp-specialised, one CTA per SM, 192 threads.
-//   warp 0 (one lane)  TMA producer: A and B tiles (128-byte swizzled rows of
-//                      k) and, for MX, the pre-arranged scale-factor chunks,
-//                      into a ring of shared-memory stages.
+// Structure: persistent, warp-specialised, one CTA per SM, 224 threads (352 with
+// eight epilogue warps).
+//   warp 0 and the     TMA producers: A and B tiles (128-byte swizzled rows of
+//   last warp          k) and, for MX, the pre-arranged scale-factor chunks,
+//   (one lane each)    into a ring of shared-memory stages; the two take
+//                      alternate k-blocks.
 //   warp 1 (one lane)  MMA issuer: copies the stage's scale factors to tensor
 //                      memory (tcgen05.cp), issues four tcgen05.mma per stage
 //                      into a TMEM accumulator, frees the stage with
 //                      tcgen05.commit; also owns TMEM alloc/dealloc.
-//   warps 2..5         epilogue: tcgen05.ld the finished accumulator (each warp
+//   warps 2..5 (2..9)  epilogue: tcgen05.ld the finished accumulator (each warp
 //                      its own 32-lane quarter), apply alpha/beta + chain, store.
 // With two accumulator buffers in TMEM the epilogue of tile i overlaps the
 // mainloop of tile i+1.
